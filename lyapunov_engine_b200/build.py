@@ -44,8 +44,8 @@ CXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wextra", "-fvisibility=hid
 
 HOST_SOURCES = ["host/block_manager.cpp", "host/scheduler.cpp", "host/step_pack.cpp", "host/bindings.cpp"]
 CORE_KERNEL_SOURCES = ["kernels/elementwise.cu", "kernels/norm.cu", "kernels/rope_kv.cu",
-                       "kernels/gemm_f32.cu", "kernels/sampling.cu", "kernels/gemm_skinny.cu", "kernels/gemm_tc.cu"
-                       ]
+                       "kernels/gemm_f32.cu", "kernels/sampling.cu", "kernels/gemm_skinny.cu", "kernels/gemm_tc.cu",
+                       "kernels/short_conv.cu", "kernels/kv_store.cu", "kernels/gemm_heads.cu"]
 ATTENTION_SOURCES = ["kernels/attention_generic.cu", "kernels/attention_mma.cu", "kernels/attention_tc.cu"]
 
 _lock = threading.Lock()
@@ -243,8 +243,8 @@ def load_core():
 
 
 def load_attention(head_dim: int):
-    if head_dim % 16 or not 16 <= head_dim <= 256:
-        raise BuildError(f"attention kernels take head sizes 16..256 in steps of 16, got {head_dim}")
+    if head_dim % 16 or not 16 <= head_dim <= 512:
+        raise BuildError(f"attention kernels take head sizes 16..512 in steps of 16, got {head_dim}")
     return load_kernels(f"attention_hd{head_dim}", ATTENTION_SOURCES, [f"-DLE_HEAD_DIM={head_dim}"])
 
 

@@ -32,10 +32,12 @@ class KVStream:
 
 @dataclass
 class CacheBinding:
-    """What one run of a layer sees of the cache."""
+    """What one run of a layer sees of the cache.  ``extra``: the state
+    buffers of the block's parts other than the mixer, by name."""
     kv: KVStream | None
     write: bool
     state: torch.Tensor | None
+    extra: dict | None = None
 
 
 class DeviceCache:
@@ -45,17 +47,18 @@ class DeviceCache:
         self.block_size = int(block_size)
         self.num_blocks = int(num_blocks)
         self.max_num_seqs = int(max_num_seqs)
-        groups = [host.CacheGroupSpec(block_size=self.block_size, window=int(g.window or 0), num_blocks=self.num_blocks)
-                  for g in model.groups]
+        groups = [host.CacheGroupSpec(block_size=self.block_size, window=int(g.window or 0), num_blocks=self.num_blocks,
+                                      chunk=int(g.chunk or 0)) for g in model.groups]
         self.manager = host.BlockSpaceManager(groups, self.max_num_seqs)
         self.streams: list[list[KVStream]] = []
         for gi, g in enumerate(model.groups):
             pools = []
             for _ in range(model.streams_per_group[gi]):
                 shape = (self.num_blocks + 1, g.num_kv_heads, self.block_size, g.head_dim)
-                pools.append(KVStream(torch.zeros(shape, dtype=runtime.dtype, device=runtime.device),
-                                      torch.zeros(shape, dtype=runtime.dtype, device=runtime.device),
-                                      self.block_size, gi))
+                k = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device)
+                # (a group without values of their own: the one pool is read as keys and as values)
+                v = torch.zeros(shape, dtype=runtime.dtype, device=runtime.device) if g.values else k
+                pools.append(KVStream(k, v, self.block_size, gi))
             self.streams.append(pools)
         self.states = [torch.zeros((self.max_num_seqs + 1, *need.shape), dtype=need.dtype or torch.float32,
                                    device=runtime.device) for need in model.states]
@@ -63,7 +66,8 @@ class DeviceCache:
         for run in model.runs:
             kv = self.streams[run.group][run.stream] if run.group is not None else None
             state = self.states[run.state] if run.state is not None else None
-            self._bindings.append(CacheBinding(kv, run.writes, state))
+            extra = {name: self.states[index] for name, index in run.extra_states}
+            self._bindings.append(CacheBinding(kv, run.writes, state, extra))
 
     def binding(self, run_index: int) -> CacheBinding:
         return self._bindings[run_index]
@@ -72,7 +76,7 @@ class DeviceCache:
         total = 0
         for pools in self.streams:
             for s in pools:
-                total += 2 * s.k.numel() * s.k.element_size()
+                total += (1 if s.v is s.k else 2) * s.k.numel() * s.k.element_size()
         for s in self.states:
             total += s.numel() * s.element_size()
         return total
@@ -82,5 +86,5 @@ class DeviceCache:
         width = 2 if dtype == torch.bfloat16 else 4
         total = 0
         for gi, g in enumerate(model.groups):
-            total += 2 * model.streams_per_group[gi] * g.num_kv_heads * block_size * g.head_dim * width
+            total += (2 if g.values else 1) * model.streams_per_group[gi] * g.num_kv_heads * block_size * g.head_dim * width
         return total

@@ -15,6 +15,8 @@ BlockSpaceManager::BlockSpaceManager(std::vector<CacheGroupSpec> groups, int num
     if (g.block_size < 1) throw std::invalid_argument("BlockSpaceManager: block_size must be >= 1");
     if (g.num_blocks < 0) throw std::invalid_argument("BlockSpaceManager: num_blocks must be >= 0");
     if (g.window < 0) throw std::invalid_argument("BlockSpaceManager: window must be >= 0");
+    if (g.chunk < 0) throw std::invalid_argument("BlockSpaceManager: chunk must be >= 0");
+    if (g.window > 0 && g.chunk > 0) throw std::invalid_argument("BlockSpaceManager: a group has a window or chunks, not both");
   }
   if (num_state_slots_ < 0) throw std::invalid_argument("BlockSpaceManager: num_state_slots must be >= 0");
   reset();
@@ -97,10 +99,12 @@ int BlockSpaceManager::release_passed(const SequencePtr &seq) {
   const int64_t computed = static_cast<int64_t>(seq->get_num_computed_tokens());
   for (size_t g = 0; g < groups_.size() && g < tables.size(); ++g) {
     const int window = groups_[g].window;
-    if (window <= 0) continue;
+    const int chunk = groups_[g].chunk;
+    if (window <= 0 && chunk <= 0) continue;
     // The next query stands at position `computed` and reads keys from
-    // computed - window + 1 on; pages wholly below that are dead.
-    const int64_t first_needed = computed - window + 1;
+    // computed - window + 1 on (from the start of its own chunk on, where the
+    // group's keys are visible chunk by chunk); pages wholly below that are dead.
+    const int64_t first_needed = window > 0 ? computed - window + 1 : computed / chunk * chunk;
     if (first_needed <= 0) continue;
     const int64_t dead_pages = first_needed / groups_[g].block_size;
     for (int64_t i = 0; i < dead_pages && i < static_cast<int64_t>(tables[g].size()); ++i) {

@@ -8,7 +8,8 @@
 // (so the order in which pages are used again is reproducible) and adds:
 //   * cache groups: layers with different needs (all keys, or a window of
 //     them) have pools and block tables of their own;
-//   * pages that a window has passed are given back while the request lives;
+//   * pages that a window has passed (or that lie before the chunk the next
+//     query stands in) are given back while the request lives;
 //   * one arithmetic for prompts, portions and decoded tokens: grow(seq, n)
 //     makes room for the first n tokens; it changes nothing when it fails;
 //   * slots for per-request state of fixed size, taken with the first page
@@ -31,6 +32,7 @@ struct CacheGroupSpec {
   int block_size{16};
   int window{0};      // 0: every key is kept; w > 0: a query at p reads keys p-w+1 .. p
   int num_blocks{0};  // pages of this group's pool
+  int chunk{0};       // c > 0: a query at p reads keys floor(p / c) * c .. p (chunks counted from position 0)
 };
 
 class BlockSpaceManager {

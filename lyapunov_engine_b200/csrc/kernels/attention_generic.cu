@@ -1,9 +1,11 @@
 // Causal grouped-query attention over the paged cache on the FP32 pipes: the
 // attention of the true 32-bit path and the plain twin of the tensor-core
 // kernels.  One formula for every cut of the work: the query token at
-// absolute position p of request b reads keys max(0, p - window + 1) .. p of
-// that request through its block table, whether the step brings a whole
-// prompt, a portion of two tokens or one decoded token.
+// absolute position p of request b reads keys first_visible_key(p, reach) .. p
+// of that request (all of them, a sliding window, or its own chunk) through
+// its block table, whether the step brings a whole prompt, a portion of two
+// tokens or one decoded token.  Scores are (q . k) * scale, times one number
+// per query head where `head_scale` is given.
 //
 // One block per (tile of 16 query tokens of one request, query head).  Keys
 // are visited in tiles of 32 from position 0 (or the window's start) with a
@@ -44,7 +46,8 @@ attention_generic_kernel(T *__restrict__ out, int64_t out_stride, const T *__res
                          const int32_t *__restrict__ block_table, int max_blocks, const int32_t *__restrict__ cu_q,
                          const int32_t *__restrict__ ctx_before, const int32_t *__restrict__ tile_request,
                          const int32_t *__restrict__ tile_q0, int num_heads, int num_kv_heads, int page_size,
-                         int num_pages, int window, float scale, int *__restrict__ status) {
+                         int num_pages, int reach, float scale, const float *__restrict__ head_scale,
+                         int *__restrict__ status) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   GenericSmem &sm = *reinterpret_cast<GenericSmem *>(smem_raw);
 
@@ -67,14 +70,14 @@ attention_generic_kernel(T *__restrict__ out, int64_t out_stride, const T *__res
 
   const int row = tid / 8, sub = tid % 8;      // this thread's query row and its lane in the row's group of 8
   const int p_row = p0 + row;
-  const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
+  const int lo_row = le::first_visible_key(p_row, reach);
+  if (head_scale) scale *= head_scale[head];
   float m_run = -INFINITY, l_run = 0.0f;
   float acc[HD / 8];
 #pragma unroll
   for (int j = 0; j < HD / 8; ++j) acc[j] = 0.0f;
 
-  int k_begin = 0;
-  if (window > 0) k_begin = max(0, p0 - window + 1) / KT * KT;
+  const int k_begin = le::first_visible_key(p0, reach) / KT * KT;
 
   for (int k0 = k_begin; k0 <= p_last; k0 += KT) {
     __syncthreads();
@@ -160,11 +163,13 @@ LE_API const char *le_last_error() { return le::error_buffer(); }
 // out: [T, num_heads * HD] with row stride out_stride; q: rows of stride
 // q_stride holding num_heads * HD query values; caches [pages, kv_heads,
 // page, HD].  tile_request / tile_q0 list the tiles of 16 query tokens.
+// `reach`: see le::first_visible_key; `head_scale`: num_heads floats or null.
 LE_API int le_attention_generic(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *k_cache,
                                 const void *v_cache, int dtype, const int32_t *block_table, int max_blocks,
                                 const int32_t *cu_q, const int32_t *ctx_before, const int32_t *tile_request,
                                 const int32_t *tile_q0, int num_tiles, int num_heads, int num_kv_heads, int page_size,
-                                int num_pages, int window, float scale, int *status, cudaStream_t stream) {
+                                int num_pages, int reach, float scale, const float *head_scale, int *status,
+                                cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_generic: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_heads > 65535) return le::invalid("le_attention_generic: too many heads for one launch");
@@ -180,7 +185,8 @@ LE_API int le_attention_generic(void *out, int64_t out_stride, const void *q, in
     kernel<<<grid, THREADS, smem, stream>>>(static_cast<T *>(out), out_stride, static_cast<const T *>(q), q_stride,    \
                                             static_cast<const T *>(k_cache), static_cast<const T *>(v_cache),          \
                                             block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0,          \
-                                            num_heads, num_kv_heads, page_size, num_pages, window, scale, status);     \
+                                            num_heads, num_kv_heads, page_size, num_pages, reach, scale, head_scale,   \
+                                            status);                                                                   \
   } while (0)
   if (dtype == LE_F32) LE_GO(float);
   else if (dtype == LE_BF16) LE_GO(__nv_bfloat16);

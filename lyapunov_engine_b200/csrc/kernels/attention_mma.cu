@@ -14,7 +14,7 @@
 // 16-byte cp.async copies into a swizzled shared-memory tile, several tiles in
 // flight, so any page size works and a page's rows need not be adjacent.
 // One formula for every cut: the query at absolute position p sees keys
-// max(0, p - window + 1) .. p of its own request.
+// le::first_visible_key(p, reach) .. p of its own request (all keys, a window, or its own chunk).
 //
 // Reference: flash_attn_v2.cu:13-212 (contiguous keys, scalar dot products,
 // top-left mask), flash_decoding.cu:13-147 (contiguous keys, every thread
@@ -235,7 +235,8 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
                          const int32_t *__restrict__ block_table, int max_blocks, const int32_t *__restrict__ cu_q,
                          const int32_t *__restrict__ ctx_before, const int32_t *__restrict__ tile_request,
                          const int32_t *__restrict__ tile_q0, int num_heads, int num_kv_heads, int page_size,
-                         int page_shift, int num_pages, int window, float scale, int *__restrict__ status) {
+                         int page_shift, int num_pages, int reach, float scale, const float *__restrict__ head_scale,
+                         int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16 *q_tile = reinterpret_cast<bf16 *>(smem_raw);
   bf16 *k_tiles = q_tile + PF_BM * HD;
@@ -262,8 +263,7 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
     const bf16 *src = q + (tok0 + (valid ? row : 0)) * q_stride + head * HD + chunk * 8;
     cp_async16(q_tile + swizzled_chunk(row, chunk) * 8, src, valid);
   }
-  int k_begin = 0;
-  if (window > 0) k_begin = max(0, p0 - window + 1) / BN * BN;
+  const int k_begin = le::first_visible_key(p0, reach) / BN * BN;
   const int k_end = p_last + 1;
   const int num_tiles = (k_end - k_begin + BN - 1) / BN;
 
@@ -284,11 +284,13 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
   const float sl2 = scale * LOG2E;
   const int row_lo = warp * 16 + g, row_hi = row_lo + 8;
   const int p_row[2] = {p0 + row_lo, p0 + row_hi};
-  const int lo_row[2] = {window > 0 ? max(0, p_row[0] - window + 1) : 0, window > 0 ? max(0, p_row[1] - window + 1) : 0};
+  const int lo_row[2] = {le::first_visible_key(p_row[0], reach), le::first_visible_key(p_row[1], reach)};
+  // one more factor on this head's scores, applied to them in 32 bits before the maximum (it may be negative)
+  const float extra = head_scale ? head_scale[head] : 1.0f;
   // what this warp's 16 rows can see at all
   const int warp_p_first = p0 + warp * 16, warp_p_last = warp_p_first + 15;
-  const int warp_lo_first = window > 0 ? max(0, warp_p_first - window + 1) : 0;
-  const int warp_lo_last = window > 0 ? max(0, warp_p_last - window + 1) : 0;
+  const int warp_lo_first = le::first_visible_key(warp_p_first, reach);
+  const int warp_lo_last = le::first_visible_key(warp_p_last, reach);
 
   for (int it = 0; it < num_tiles; ++it) {
     const int k0 = k_begin + it * BN;
@@ -318,6 +320,10 @@ attention_prefill_kernel(bf16 *__restrict__ out, int64_t out_stride, const bf16 
 #pragma unroll
       for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
       scores<BN / 8>(s, qf, k_tile, k_at);
+      if (head_scale) {
+#pragma unroll
+        for (int nt = 0; nt < BN / 8; ++nt) s[nt][0] *= extra, s[nt][1] *= extra, s[nt][2] *= extra, s[nt][3] *= extra;
+      }
       // only tiles that cross the causal diagonal or the window's edge need the mask
       const bool needs_mask = k0 + BN - 1 > warp_p_first || k0 < warp_lo_last;
       if (needs_mask) {
@@ -417,8 +423,8 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
                         const bf16 *__restrict__ v_cache, const int32_t *__restrict__ block_table, int max_blocks,
                         const int32_t *__restrict__ cu_q, const int32_t *__restrict__ ctx_before,
                         const int32_t *__restrict__ requests, int num_heads, int num_kv_heads, int page_size,
-                        int page_shift, int num_pages, int window, float scale, int num_splits, int cluster_merge,
-                        int *__restrict__ status) {
+                        int page_shift, int num_pages, int reach, float scale, const float *__restrict__ head_scale,
+                        int num_splits, int cluster_merge, int *__restrict__ status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   // (the kernel before this one wrote the queries and the newest key and value of every request; what is
   // read before wait_for_predecessor() below is older than that: the step's integers and keys of earlier steps)
@@ -457,7 +463,7 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
     }
     return;
   }
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int lo = le::first_visible_key(p, reach);
   const int total = p + 1 - lo;
   int per_split = (total + num_splits - 1) / num_splits;
   per_split = (per_split + DC_TILE - 1) / DC_TILE * DC_TILE;
@@ -520,6 +526,13 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
   const float sl2 = scale * LOG2E;
   const bool upper_rows = heads_here > 8;     // rows 8..15 of the MMA are padding for small groups
+  // one more factor on each head's scores (rows g and g + 8 of the MMA are heads h0 + g and h0 + g + 8), applied
+  // in 32 bits before the maximum (it may be negative)
+  float extra[2] = {1.0f, 1.0f};
+  if (head_scale) {
+    if (g < heads_here) extra[0] = head_scale[h0 + g];
+    if (g + 8 < heads_here) extra[1] = head_scale[h0 + g + 8];
+  }
 
   for (int it = 0; it < my_tiles; ++it) {
     cp_async_wait<DC_STAGES - 2>();
@@ -533,6 +546,10 @@ attention_decode_kernel(bf16 *__restrict__ out, int64_t out_stride, float *__res
 #pragma unroll
     for (int nt = 0; nt < DC_TILE / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
     scores<DC_TILE / 8>(s, qf, k_tile, k_at);
+    if (head_scale) {
+#pragma unroll
+      for (int nt = 0; nt < DC_TILE / 8; ++nt) s[nt][0] *= extra[0], s[nt][1] *= extra[0], s[nt][2] *= extra[1], s[nt][3] *= extra[1];
+    }
     const bool full = k0 + DC_TILE <= k_end;
     if (!full) {
 #pragma unroll
@@ -752,7 +769,7 @@ LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *
                                      const void *v_cache, const int32_t *block_table, int max_blocks, const int32_t *cu_q,
                                      const int32_t *ctx_before, const int32_t *tile_request, const int32_t *tile_q0,
                                      int num_tiles, int num_heads, int num_kv_heads, int page_size, int num_pages,
-                                     int window, float scale, int *status, cudaStream_t stream) {
+                                     int reach, float scale, const float *head_scale, int *status, cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_prefill_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_heads > 65535) return le::invalid("le_attention_prefill_bf16: too many heads for one launch");
@@ -766,7 +783,7 @@ LE_API int le_attention_prefill_bf16(void *out, int64_t out_stride, const void *
   attention_prefill_kernel<<<grid, PF_THREADS, smem, stream>>>(
       static_cast<bf16 *>(out), out_stride, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
       static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
-      num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, status);
+      num_kv_heads, page_size, page_shift_of(page_size), num_pages, reach, scale, head_scale, status);
   return le::launched();
 }
 
@@ -867,7 +884,7 @@ struct DecodeForm {
   static int launch(dim3 grid, cudaStream_t stream, void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
                     const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks, const int32_t *cu_q,
                     const int32_t *ctx_before, const int32_t *requests, int num_requests, int num_heads, int num_kv_heads,
-                    int page_size, int num_pages, int window, float scale, int num_splits, int *status) {
+                    int page_size, int num_pages, int reach, float scale, const float *head_scale, int num_splits, int *status) {
     if (!ready()) return le::invalid("le_attention_decode_bf16: cannot get %zu bytes of shared memory", smem());
     if (cluster_fits(num_splits)) {
       // the splits of a (request, kv head) as one cluster: merged through shared memory, no scratch, no second kernel
@@ -876,7 +893,7 @@ struct DecodeForm {
                                         static_cast<float *>(nullptr), static_cast<const bf16 *>(q), q_stride,
                                         static_cast<const bf16 *>(k_cache), static_cast<const bf16 *>(v_cache), block_table,
                                         max_blocks, cu_q, ctx_before, requests, num_heads, num_kv_heads, page_size,
-                                        page_shift_of(page_size), num_pages, window, scale, num_splits, 1, status);
+                                        page_shift_of(page_size), num_pages, reach, scale, head_scale, num_splits, 1, status);
     }
     if (num_splits > 1 && scratch == nullptr) return le::invalid("le_attention_decode_bf16: splitting the keys %d ways needs scratch memory", num_splits);
     if (reinterpret_cast<uintptr_t>(scratch) % 8) return le::invalid("le_attention_decode_bf16: the scratch memory must start on an 8-byte boundary");
@@ -885,7 +902,7 @@ struct DecodeForm {
     int rc = le::launch_chained(attention_decode_kernel<TILE>, grid, dim3(DC_THREADS), smem(), stream, static_cast<bf16 *>(out), out_stride,
                                 part_o, part_ml, static_cast<const bf16 *>(q), q_stride, static_cast<const bf16 *>(k_cache),
                                 static_cast<const bf16 *>(v_cache), block_table, max_blocks, cu_q, ctx_before, requests, num_heads,
-                                num_kv_heads, page_size, page_shift_of(page_size), num_pages, window, scale, num_splits, 0, status);
+                                num_kv_heads, page_size, page_shift_of(page_size), num_pages, reach, scale, head_scale, num_splits, 0, status);
     if (rc != 0 || num_splits == 1) return rc;
     dim3 mgrid(num_heads, num_requests);
     return le::launch_chained(attention_merge_kernel, mgrid, dim3(HD < 32 ? 32 : (HD > 128 ? 128 : HD)),
@@ -920,6 +937,7 @@ LE_API int le_attention_decode_resident_blocks(int num_splits, int small) {
 // it requests 0 .. num_requests-1 are taken.  `scratch` holds
 // le_attention_decode_scratch_floats(...) floats; it is used when the keys are
 // cut into more splits than a thread-block cluster merges by itself.
+// `reach`: see le::first_visible_key; `head_scale`: one more factor per query head on its scores, or null.
 // `form`: 0 lets the number of blocks decide between the usual form of the kernel and the one with 16-key tiles
 // (see small_form); 1 asks for the usual form, 2 for the small one where the head size has it (a caller that pads
 // the step with dummy requests knows how many of the blocks are real; the grid does not show it).
@@ -927,7 +945,8 @@ LE_API int le_attention_decode_bf16_form(void *out, int64_t out_stride, float *s
                                          const void *k_cache, const void *v_cache, const int32_t *block_table, int max_blocks,
                                          const int32_t *cu_q, const int32_t *ctx_before, const int32_t *requests,
                                          int num_requests, int num_heads, int num_kv_heads, int page_size, int num_pages,
-                                         int window, float scale, int num_splits, int form, int *status, cudaStream_t stream) {
+                                         int reach, float scale, const float *head_scale, int num_splits, int form, int *status,
+                                         cudaStream_t stream) {
   if (num_requests <= 0) return 0;
   if (num_kv_heads <= 0 || num_heads % num_kv_heads) return le::invalid("le_attention_decode_bf16: %d heads do not divide into %d groups", num_heads, num_kv_heads);
   if (num_splits < 1 || num_splits > MERGE_MAX_SPLITS) return le::invalid("le_attention_decode_bf16: %d splits (1..%d)", num_splits, MERGE_MAX_SPLITS);
@@ -939,11 +958,11 @@ LE_API int le_attention_decode_bf16_form(void *out, int64_t out_stride, float *s
                                : (form == 2 && DC_TILE_DEFAULT == 32 && small_tiles_enabled() && DecodeForm<16>::ready());
   if (small)
     return DecodeForm<16>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
-                                  ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, window, scale,
-                                  num_splits, status);
+                                  ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, reach, scale,
+                                  head_scale, num_splits, status);
   return DecodeForm<DC_TILE_DEFAULT>::launch(grid, stream, out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table,
                                              max_blocks, cu_q, ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size,
-                                             num_pages, window, scale, num_splits, status);
+                                             num_pages, reach, scale, head_scale, num_splits, status);
 }
 
 LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratch, const void *q, int64_t q_stride,
@@ -953,7 +972,7 @@ LE_API int le_attention_decode_bf16(void *out, int64_t out_stride, float *scratc
                                     int window, float scale, int num_splits, int *status, cudaStream_t stream) {
   return le_attention_decode_bf16_form(out, out_stride, scratch, q, q_stride, k_cache, v_cache, block_table, max_blocks, cu_q,
                                        ctx_before, requests, num_requests, num_heads, num_kv_heads, page_size, num_pages, window,
-                                       scale, num_splits, 0, status, stream);
+                                       scale, nullptr, num_splits, 0, status, stream);
 }
 
 // ---------------------------------------------------------------- no allocation

@@ -42,7 +42,7 @@
 // status word, lets copies in flight land, frees its tensor memory and returns.
 //
 // Same contract as the mma.sync kernel in attention_mma.cu (query at absolute
-// position p sees keys max(0, p - window + 1) .. p of its own request through
+// position p sees keys le::first_visible_key(p, reach) .. p of its own request through
 // the block table), which stays for other head and page sizes.
 // Reference: flash_attn_v2.cu:13-212 (contiguous keys, scalar products).
 #include "tc_common.cuh"
@@ -93,7 +93,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                     const int32_t *__restrict__ block_table, int max_blocks, const int32_t *__restrict__ cu_q,
                     const int32_t *__restrict__ ctx_before, const int32_t *__restrict__ tile_request,
                     const int32_t *__restrict__ tile_q0, int num_heads, int num_kv_heads, int page_size, int page_shift,
-                    int num_pages, int window, float scale, int *__restrict__ status) {
+                    int num_pages, int reach, float scale, const float *__restrict__ head_scale, int *__restrict__ status) {
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~uintptr_t(1023));
   unsigned char *q_smem = smem;                // [2 heads]
@@ -126,8 +126,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   const int tok0 = cu_q[b] + q0;
   const int p0 = ctx_before[b] + q0;
   const int p_last = p0 + rows - 1;
-  int k_begin = 0;
-  if (window > 0) k_begin = max(0, p0 - window + 1) / BN * BN;
+  const int k_begin = le::first_visible_key(p0, reach) / BN * BN;
   const int num_tiles = (p_last + 1 - k_begin + BN - 1) / BN;
   const int32_t *table = block_table + static_cast<int64_t>(b) * max_blocks;
 
@@ -320,11 +319,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const int g = warp >> 2;
     const int r = quarter * 32 + lane;
     const int p_row = p0 + r;
-    const int lo_row = window > 0 ? max(0, p_row - window + 1) : 0;
+    const int lo_row = le::first_visible_key(p_row, reach);
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     const uint32_t s_col = lane_base + g * BN, o_col = lane_base + O_COL + g * HD;
     const uint32_t p_tmem = lane_base + p_col(g);
-    const float sl2 = scale * LOG2E;
+    // (one more factor per head, where given, must be positive here: the running maximum is kept in exponent units)
+    const float sl2 = scale * LOG2E * (head_scale ? head_scale[head0 + g] : 1.0f);
     const float2 sl2_2 = make_float2(sl2, sl2);
     float m_run = -INFINITY, l_run = 0.0f;      // m_run in exponent units (score * scale * log2 e)
     bool ok = true;
@@ -450,7 +450,7 @@ LE_API int le_attention_prefill_tc_bf16(void *out, int64_t out_stride, const voi
                                         int q_width, const void *k_cache, const void *v_cache, const int32_t *block_table,
                                         int max_blocks, const int32_t *cu_q, const int32_t *ctx_before,
                                         const int32_t *tile_request, const int32_t *tile_q0, int num_tiles, int num_heads,
-                                        int num_kv_heads, int page_size, int num_pages, int window, float scale, int *status,
+                                        int num_kv_heads, int page_size, int num_pages, int reach, float scale, const float *head_scale, int *status,
                                         cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (!le_attention_tc_available(page_size)) return le::invalid("le_attention_prefill_tc_bf16: pages of %d keys are not supported (8..128, a power of two)", page_size);
@@ -474,7 +474,7 @@ LE_API int le_attention_prefill_tc_bf16(void *out, int64_t out_stride, const voi
   dim3 grid(num_kv_heads * ((group + 1) / 2), num_tiles);   // two heads of a group per block
   return le::launch_chained(attention_tc_kernel, grid, dim3(THREADS), smem, stream, map_q, map_k, map_v, static_cast<bf16 *>(out),
                             out_stride, block_table, max_blocks, cu_q, ctx_before, tile_request, tile_q0, num_heads,
-                            num_kv_heads, page_size, tc_page_shift_of(page_size), num_pages, window, scale, status);
+                            num_kv_heads, page_size, tc_page_shift_of(page_size), num_pages, reach, scale, head_scale, status);
 }
 
 #else

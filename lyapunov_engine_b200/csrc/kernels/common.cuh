@@ -134,6 +134,17 @@ __device__ __forceinline__ float cluster_peer_f32(const float *mine, unsigned ra
   return v;
 }
 
+// Which keys a query at position p sees besides "none after itself", as one
+// integer `reach`: 0: every key; r > 0: the last r keys (p - r + 1 .. p, a
+// sliding window); r < 0: the keys of its own chunk of -r positions
+// (floor(p / -r) * -r .. p; chunks are counted from position 0 of the request).
+// The first visible key never decreases as p grows.
+__host__ __device__ __forceinline__ int first_visible_key(int p, int reach) {
+  if (reach > 0) return p - reach + 1 > 0 ? p - reach + 1 : 0;
+  if (reach < 0) return p / (-reach) * (-reach);
+  return 0;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T x);
 template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }

@@ -1,4 +1,5 @@
-// Embedding gather, SwiGLU and small helpers.
+// Embedding gather (optionally with a sinusoidal position vector added),
+// gated activations, the per-head output gate and small helpers.
 //
 // Reference counterparts: nn.Embedding (python/lyapunov_engine/models/llama.py:172,205)
 // and swiglu_kernel (csrc/kernels/fused_rmsnorm_swiglu.cu:152-179).
@@ -26,6 +27,66 @@ __global__ void embed_kernel(float *__restrict__ out, const T *__restrict__ tabl
   }
   const T *src = table + static_cast<int64_t>(id) * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = le::to_f32(src[i]);
+}
+
+// The same with a sinusoidal position vector added in 32 bits: for the token at
+// position p, entry 2i gets sin(p * rate[i]) and entry 2i + 1 the cosine of the
+// same angle.  `rates` holds ceil(hidden / 2) floats; angle, sine and cosine
+// are 32-bit (sinf / cosf, not the fast approximations).
+template <typename T>
+__global__ void embed_sinusoid_kernel(float *__restrict__ out, const T *__restrict__ table, const int32_t *__restrict__ ids,
+                                      const int32_t *__restrict__ positions, const float *__restrict__ rates, int hidden,
+                                      int vocab, int *__restrict__ status) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const float p = static_cast<float>(positions[t]);
+  float *dst = out + static_cast<int64_t>(t) * hidden;
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_TOKEN);
+  const T *src = table + static_cast<int64_t>(bad ? 0 : id) * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float angle = p * rates[i >> 1];
+    const float wave = (i & 1) ? cosf(angle) : sinf(angle);
+    dst[i] = bad ? 0.0f : le::to_f32(src[i]) + wave;
+  }
+}
+
+// Gated activations of a fused gate/up product, in 32-bit, rounded once.
+//   kind 0: silu(g) * u
+//   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(alpha * g') * (u' + 1)
+__device__ __forceinline__ float glu_value(float g, float u, int kind, float alpha, float limit) {
+  if (kind == 0) return g / (1.0f + expf(-g)) * u;
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
+template <typename T>
+__global__ void glu_kernel(T *__restrict__ out, const T *__restrict__ gu, int64_t total, int inter, int kind, float alpha,
+                           float limit) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int64_t t = idx / inter;
+  const int i = static_cast<int>(idx - t * inter);
+  const float g = le::to_f32(gu[t * 2 * inter + i]);
+  const float u = le::to_f32(gu[t * 2 * inter + inter + i]);
+  out[idx] = le::from_f32<T>(glu_value(g, u, kind, alpha, limit));
+}
+
+// x[t, h, :] *= sigmoid(gate[t, h]): one number per token and head scales that
+// head's `head_width` values.  Sigmoid and product are 32-bit, rounded once.
+template <typename T>
+__global__ void head_gate_kernel(T *__restrict__ x, int64_t x_stride, const T *__restrict__ gate, int64_t gate_stride,
+                                 int num_heads, int head_width) {
+  const int t = blockIdx.x;
+  const int row = num_heads * head_width;
+  for (int i = threadIdx.x; i < row; i += blockDim.x) {
+    const float g = le::to_f32(gate[t * gate_stride + i / head_width]);
+    T *p = x + t * x_stride + i;
+    *p = le::from_f32<T>(le::to_f32(*p) / (1.0f + expf(-g)));
+  }
 }
 
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], in 32-bit, rounded once.
@@ -106,6 +167,42 @@ LE_API int le_embed(float *out, const void *table, int table_dtype, const int32_
   LE_DISPATCH_DTYPE(table_dtype, T,
                     return le::launch_chained(embed_kernel<T>, dim3(num_tokens), dim3(threads), 0, stream, out,
                                               static_cast<const T *>(table), ids, hidden, vocab, status));
+}
+
+// The embedding with the sinusoidal position vector (see embed_sinusoid_kernel).
+LE_API int le_embed_sinusoid(float *out, const void *table, int table_dtype, const int32_t *ids, const int32_t *positions,
+                             const float *rates, int num_tokens, int hidden, int vocab, int *status, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  LE_DISPATCH_DTYPE(table_dtype, T,
+                    return le::launch_chained(embed_sinusoid_kernel<T>, dim3(num_tokens), dim3(threads), 0, stream, out,
+                                              static_cast<const T *>(table), ids, positions, rates, hidden, vocab, status));
+}
+
+// out[T, I] from gate_up[T, 2 I] (gate columns first) by the activation `kind` (see glu_value).
+LE_API int le_glu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, int kind, float alpha, float limit,
+                  cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  if (kind != 0 && kind != 1) return le::invalid("le_glu: unknown activation %d", kind);
+  const int64_t total = static_cast<int64_t>(num_tokens) * inter;
+  const int threads = 256;
+  const int64_t blocks = (total + threads - 1) / threads;
+  if (blocks > 2147483647LL) return le::invalid("le_glu: %lld elements are too many for one launch", (long long)total);
+  LE_DISPATCH_DTYPE(dtype, T,
+                    glu_kernel<T><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+                        static_cast<T *>(out), static_cast<const T *>(gate_up), total, inter, kind, alpha, limit));
+  return le::launched();
+}
+
+// x: [T, num_heads * head_width] with row stride x_stride; gate: rows of stride gate_stride holding num_heads values.
+LE_API int le_head_gate(void *x, int64_t x_stride, const void *gate, int64_t gate_stride, int dtype, int num_tokens,
+                        int num_heads, int head_width, cudaStream_t stream) {
+  if (num_tokens <= 0) return 0;
+  LE_DISPATCH_DTYPE(dtype, T,
+                    head_gate_kernel<T><<<num_tokens, 256, 0, stream>>>(static_cast<T *>(x), x_stride,
+                                                                        static_cast<const T *>(gate), gate_stride,
+                                                                        num_heads, head_width));
+  return le::launched();
 }
 
 LE_API int le_swiglu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, cudaStream_t stream) {

@@ -3,6 +3,9 @@
 //   resid[r] += delta[0][r] + delta[1][r] + ...   (when delta is given)
 //   out[r]    = resid[r] * rsqrt(mean(resid[r]^2) + eps) * weight
 //
+// With `groups` > 1 a row is cut into that many equal consecutive parts and
+// each part is divided by its own root mean square (one block per row and part).
+//
 // delta is the output of the sub-layer before the norm: one tensor in the
 // activations' type, or the float32 partial sums of a split-K product, which
 // are added here in their fixed order.
@@ -58,14 +61,18 @@ __device__ __forceinline__ void store_vec(T *p, const float (&src)[VEC]) {
 template <typename TO, typename TD, int VEC, int PER_THREAD, int PARTIALS>
 __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, const TD *__restrict__ delta,
                                int num_partials, int64_t partial_stride, const float *__restrict__ weight,
-                               const int32_t *__restrict__ rows, float eps, int hidden) {
+                               const int32_t *__restrict__ rows, float eps, int hidden, int row_width) {
+  // `hidden`: the values that share one root mean square (the row, or one of its equal parts: blockIdx.y);
+  // `row_width`: the values of a whole row
   __shared__ float scratch[33];
   le::let_successor_start();
   le::wait_for_predecessor();
   const int64_t src_row = rows ? rows[blockIdx.x] : blockIdx.x;
-  float *x = resid + src_row * hidden;
-  const TD *d = delta ? delta + src_row * hidden : nullptr;
-  TO *o = out + static_cast<int64_t>(blockIdx.x) * hidden;
+  const int64_t part = static_cast<int64_t>(blockIdx.y) * hidden;
+  float *x = resid + src_row * row_width + part;
+  const TD *d = delta ? delta + src_row * row_width + part : nullptr;
+  TO *o = out + static_cast<int64_t>(blockIdx.x) * row_width + part;
+  weight += part;
   const bool write_back = (d != nullptr) && (rows == nullptr);
 
   if constexpr (PER_THREAD > 0 && PARTIALS > 0) {
@@ -173,13 +180,14 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
 
 template <typename TO, typename TD>
 int launch(void *out, float *resid, const void *delta, int num_partials, int64_t partial_stride, const float *weight,
-           const int32_t *rows, float eps, int num_rows, int hidden, cudaStream_t stream) {
+           const int32_t *rows, float eps, int num_rows, int row_width, int groups, cudaStream_t stream) {
+  const int hidden = row_width / groups;
   int threads = 32;
   while (threads < 512 && threads * 8 < hidden) threads *= 2;
 #define LE_NORM_P(VEC, PER, PARTIALS)                                                                                  \
-  return le::launch_chained(rmsnorm_kernel<TO, TD, VEC, PER, PARTIALS>, dim3(num_rows), dim3(threads), 0, stream,      \
+  return le::launch_chained(rmsnorm_kernel<TO, TD, VEC, PER, PARTIALS>, dim3(num_rows, groups), dim3(threads), 0, stream, \
                             static_cast<TO *>(out), resid, static_cast<const TD *>(delta), num_partials, partial_stride, \
-                            weight, rows, eps, hidden)
+                            weight, rows, eps, hidden, row_width)
 #define LE_NORM(VEC, PER)                                                                                               \
   do {                                                                                                                  \
     if (PER > 0 && PER <= 2) {                                                                                          \
@@ -205,16 +213,19 @@ int launch(void *out, float *resid, const void *delta, int num_partials, int64_t
 
 }  // namespace
 
+// `groups`: equal consecutive parts of a row, each with its own root mean square (1: the whole row).
 // `out_dtype` is the type of `out`; `delta_dtype` that of `delta`, which holds
 // `num_partials` tensors of the residual stream's shape, `partial_stride`
 // elements apart.
 LE_API int le_rmsnorm(void *out, int out_dtype, float *resid, const void *delta, int delta_dtype, int num_partials,
                       int64_t partial_stride, const float *weight, const int32_t *rows, float eps, int num_rows, int hidden,
-                      cudaStream_t stream) {
+                      int groups, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
   if (hidden <= 0) return le::invalid("le_rmsnorm: hidden must be positive");
+  if (groups < 1 || groups > 65535 || hidden % groups)
+    return le::invalid("le_rmsnorm: a row of %d values does not divide into %d equal parts", hidden, groups);
   if (delta != nullptr && num_partials < 1) return le::invalid("le_rmsnorm: num_partials must be at least 1");
-#define LE_GO(TO, TD) return launch<TO, TD>(out, resid, delta, num_partials, partial_stride, weight, rows, eps, num_rows, hidden, stream)
+#define LE_GO(TO, TD) return launch<TO, TD>(out, resid, delta, num_partials, partial_stride, weight, rows, eps, num_rows, hidden, groups, stream)
   if (out_dtype == LE_F32 && (delta == nullptr || delta_dtype == LE_F32)) LE_GO(float, float);
   if (out_dtype == LE_BF16 && (delta == nullptr || delta_dtype == LE_BF16)) LE_GO(__nv_bfloat16, __nv_bfloat16);
   if (out_dtype == LE_BF16 && delta_dtype == LE_F32) LE_GO(__nv_bfloat16, float);

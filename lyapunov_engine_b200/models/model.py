@@ -21,6 +21,8 @@ class CacheGroupPlan:
     num_kv_heads: int
     head_dim: int
     window: int | None
+    chunk: int | None = None
+    values: bool = True      # False: one pool per run serves as keys and as values
 
 
 @dataclass(frozen=True)
@@ -30,6 +32,7 @@ class RunPlan:
     stream: int | None       # which K/V pool pair of the group it uses
     writes: bool             # False when it reads the pages another run writes
     state: int | None        # index of its state buffer (None: no state)
+    extra_states: tuple = () # (name, index of the state buffer) of what other parts of the block keep
 
 
 class Model:
@@ -45,7 +48,7 @@ class Model:
         self.runs: list[RunPlan] = []
         self._plan_cache()
         # query-tile sizes that the mixers' kernels want listed in every step's integers
-        self.tile_sizes: list[int] = sorted({int(t) for b in self.blocks for t in b.mixer.tile_sizes()})
+        self.tile_sizes: list[int] = sorted({int(t) for b in self.blocks for t in b.tile_sizes()})
         self._decode_variants: dict[tuple, tuple] = {}
 
     # ---- what the cache must hold
@@ -69,7 +72,7 @@ class Model:
                         raise ValueError(f"run order entry {index} cannot read the cache of entry {src}: different geometry")
                     group, stream, writes = other.group, other.stream, False
                 else:
-                    plan = CacheGroupPlan(need.num_kv_heads, need.head_dim, need.window)
+                    plan = CacheGroupPlan(need.num_kv_heads, need.head_dim, need.window, need.chunk, need.values)
                     if plan not in self.groups:
                         self.groups.append(plan)
                         self.streams_per_group.append(0)
@@ -82,7 +85,11 @@ class Model:
             if state is not None:
                 state_index = len(self.states)
                 self.states.append(state)
-            self.runs.append(RunPlan(run.layer, group, stream, writes, state_index))
+            extra = []
+            for name, extra_need in self.blocks[run.layer].extra_state_needs().items():
+                extra.append((name, len(self.states)))
+                self.states.append(extra_need)
+            self.runs.append(RunPlan(run.layer, group, stream, writes, state_index, tuple(extra)))
 
     # ---- tensors
     def parts(self):

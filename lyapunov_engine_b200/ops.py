@@ -70,7 +70,18 @@ _CORE_SIGNATURES = {
     "le_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
     "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_float, c_int,
-                   c_int, c_void_p],
+                   c_int, c_int, c_void_p],
+    "le_embed_sinusoid": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
+    "le_head_gate": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
+    "le_short_conv": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                      c_int, c_int, c_int, c_void_p],
+    "le_kv_store": [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                    c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_latent_norm_store": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_gemm_heads": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p],
     "le_gemm_tc_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
                         c_void_p, c_void_p],
     "le_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
@@ -89,7 +100,7 @@ _CORE_SIGNATURES = {
 _ATTENTION_SIGNATURES = {
     "le_attention_generic": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int,
                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_float, c_void_p, c_void_p],
+                             c_float, c_void_p, c_void_p, c_void_p],
 }
 
 
@@ -131,16 +142,16 @@ def attention_lib(head_dim: int):
 _EXTRA_ATTENTION_SIGNATURES: dict[str, list] = {
     "le_attention_prefill_bf16": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                  c_void_p, c_void_p],
+                                  c_void_p, c_void_p, c_void_p],
     "le_attention_prefill_tc_bf16": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                     c_int, c_float, c_void_p, c_void_p],
+                                     c_int, c_float, c_void_p, c_void_p, c_void_p],
     "le_attention_decode_bf16": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                                  c_int, c_void_p, c_void_p],
     "le_attention_decode_bf16_form": [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int,
                                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                                      c_int, c_int, c_void_p, c_void_p],
+                                      c_void_p, c_int, c_int, c_void_p, c_void_p],
 }
 
 
@@ -219,6 +230,110 @@ def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> None:
     _check(core().le_swiglu(_ptr(out), _ptr(gate_up), dtype_code(out.dtype), T, I, _stream()), "le_swiglu")
 
 
+GLU_SILU, GLU_CLAMPED = 0, 1
+
+
+def glu(out: torch.Tensor, gate_up: torch.Tensor, kind: int = GLU_SILU, alpha: float = 1.0, limit: float = 0.0) -> None:
+    """out[t, i] from gate g = gate_up[t, i] and u = gate_up[t, I + i].
+    GLU_SILU: silu(g) * u.  GLU_CLAMPED: g' = min(g, limit), u' = clamp(u,
+    -limit, limit); g' * sigmoid(alpha * g') * (u' + 1)."""
+    _need_cuda(out, gate_up)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and out.is_contiguous() and gate_up.is_contiguous() and out.dtype == gate_up.dtype
+    _check(core().le_glu(_ptr(out), _ptr(gate_up), dtype_code(out.dtype), T, I, int(kind), float(alpha), float(limit),
+                         _stream()), "le_glu")
+
+
+def embed_sinusoid(out_resid, table, ids, positions, rates, status) -> None:
+    """out_resid[t] (float32) = table[ids[t]] + s(positions[t]), where entry 2i of
+    s(p) is sin(p * rates[i]) and entry 2i + 1 is cos(p * rates[i])."""
+    _need_cuda(out_resid, table, ids, positions, rates)
+    T, H = out_resid.shape
+    assert out_resid.dtype == torch.float32 and ids.dtype == torch.int32 and positions.dtype == torch.int32
+    assert table.shape[1] == H and out_resid.is_contiguous() and table.is_contiguous()
+    assert rates.dtype == torch.float32 and rates.is_contiguous() and rates.numel() >= (H + 1) // 2
+    _check(core().le_embed_sinusoid(_ptr(out_resid), _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(positions),
+                                    _ptr(rates), T, H, table.shape[0], _ptr(status), _stream()), "le_embed_sinusoid")
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, num_heads: int, head_width: int) -> None:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place; ``gate`` may be a column
+    range of a wider buffer."""
+    _need_cuda(x, gate)
+    assert x.dtype == gate.dtype and x.stride(1) == 1 and gate.stride(1) == 1 and x.shape[1] == num_heads * head_width
+    assert gate.shape == (x.shape[0], num_heads)
+    _check(core().le_head_gate(_ptr(x), x.stride(0), _ptr(gate), gate.stride(0), dtype_code(x.dtype), x.shape[0],
+                               num_heads, head_width, _stream()), "le_head_gate")
+
+
+SHORT_CONV_TILE = 16
+SHORT_CONV_MAX_TAPS = 17
+
+
+def short_conv(out, h, w_taps, state, state_slots, cu_q, tile_request, tile_q0, num_tiles) -> None:
+    """out = h + causal convolution of h over time per channel, continuing
+    each request from its state row.  ``w_taps``: float32 [taps, channels];
+    ``state``: float32 [rows, taps - 1, channels] (None when taps is 1), row
+    ``state_slots[b]`` holds request b's last taps - 1 inputs and is brought up
+    to date; the tiles list SHORT_CONV_TILE tokens each."""
+    _need_cuda(out, h, w_taps, state, state_slots, cu_q)
+    T, C = h.shape
+    taps = w_taps.shape[0]
+    assert out.shape == h.shape and out.dtype == h.dtype and out.is_contiguous() and h.is_contiguous()
+    assert w_taps.dtype == torch.float32 and w_taps.is_contiguous() and w_taps.shape[1] == C
+    rows = 0
+    if taps > 1:
+        assert state is not None and state.dtype == torch.float32 and state.is_contiguous()
+        assert tuple(state.shape[1:]) == (taps - 1, C)
+        rows = state.shape[0]
+    _check(core().le_short_conv(_ptr(out), _ptr(h), dtype_code(h.dtype), _ptr(w_taps), _ptr(state) if taps > 1 else None,
+                                rows, _ptr(state_slots), _ptr(cu_q), _ptr(tile_request), _ptr(tile_q0), num_tiles,
+                                SHORT_CONV_TILE, C, taps, _stream()), "le_short_conv")
+
+
+def kv_store(src, k_col, v_col, k_cache, v_cache, positions, request_of_token, block_table, num_kv_heads, head_dim,
+             page_size, status) -> None:
+    """Copies keys (columns k_col ..) and values (columns v_col ..) of the rows
+    of ``src`` into the paged cache, unrotated."""
+    _need_cuda(src, k_cache, v_cache, positions, block_table)
+    assert src.stride(1) == 1 and k_cache.dtype == src.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.shape[1:] == (num_kv_heads, page_size, head_dim) and block_table.is_contiguous()
+    _check(core().le_kv_store(_ptr(src), src.stride(0), k_col, v_col, _ptr(k_cache), _ptr(v_cache), dtype_code(src.dtype),
+                              _ptr(positions), _ptr(request_of_token), _ptr(block_table), block_table.shape[1],
+                              src.shape[0], num_kv_heads, head_dim, page_size, k_cache.shape[0], _ptr(status), _stream()),
+           "le_kv_store")
+
+
+def latent_norm_store(src, col, rank, weight, eps, cache, positions, request_of_token, block_table, page_size, status) -> None:
+    """Columns col .. col + rank of each row of ``src``, divided by their root
+    mean square and multiplied by ``weight`` (32-bit), into the paged pool
+    ``cache`` [pages, 1, page, padded rank]; the padding columns get zeros."""
+    _need_cuda(src, weight, cache, positions, block_table)
+    assert src.stride(1) == 1 and cache.dtype == src.dtype and cache.is_contiguous() and block_table.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.numel() == rank
+    assert cache.shape[1] == 1 and cache.shape[2] == page_size and cache.shape[3] >= rank
+    _check(core().le_latent_norm_store(_ptr(src), src.stride(0), col, rank, cache.shape[3], _ptr(weight), float(eps),
+                                       _ptr(cache), dtype_code(src.dtype), _ptr(positions), _ptr(request_of_token),
+                                       _ptr(block_table), block_table.shape[1], src.shape[0], page_size, cache.shape[0],
+                                       _ptr(status), _stream()), "le_latent_norm_store")
+
+
+def gemm_heads(out, a, w, gate=None) -> None:
+    """One product per head: out[t, h, :] = w[h] @ a[t, h, :] (w: [heads, N,
+    K]), times sigmoid(gate[t, h]) where ``gate`` is given.  ``a``, ``out`` and
+    ``gate`` may be column ranges of wider buffers (rows of any stride)."""
+    _need_cuda(out, a, w, gate)
+    heads, N, K = w.shape
+    M = a.shape[0]
+    assert a.shape[1] == heads * K and out.shape == (M, heads * N) and a.stride(1) == 1 and out.stride(1) == 1
+    assert w.is_contiguous() and a.dtype == w.dtype == out.dtype
+    if gate is not None:
+        assert gate.shape == (M, heads) and gate.stride(1) == 1 and gate.dtype == a.dtype
+    _check(core().le_gemm_heads(_ptr(out), out.stride(0), _ptr(a), a.stride(0), _ptr(w), _ptr(gate),
+                                gate.stride(0) if gate is not None else 0, dtype_code(a.dtype), M, heads, N, K, _stream()),
+           "le_gemm_heads")
+
+
 def convert(out: torch.Tensor, src: torch.Tensor) -> None:
     _need_cuda(out, src)
     assert out.numel() == src.numel() and out.is_contiguous() and src.is_contiguous()
@@ -226,8 +341,11 @@ def convert(out: torch.Tensor, src: torch.Tensor) -> None:
                              _stream()), "le_convert")
 
 
-def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, rows=None) -> None:
+def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor, eps: float, rows=None,
+            groups: int = 1) -> None:
     """resid += delta (when given and ``rows`` is None); out = rmsnorm(resid) * weight.
+    ``groups`` > 1: each of that many equal consecutive parts of a row is
+    divided by its own root mean square.
     ``delta`` has the residual stream's shape [T, H] in the activations' type,
     or is float32 [S, T, H]: the partial sums of a split-K product, added in
     order.  With ``rows`` (int32 indices) only those rows are normed, into
@@ -251,7 +369,7 @@ def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor,
     else:
         assert n == resid.shape[0]
     _check(core().le_rmsnorm(_ptr(out), dtype_code(out.dtype), _ptr(resid), _ptr(delta), dcode, parts, stride,
-                             _ptr(weight), _ptr(rows), float(eps), n, H, _stream()), "le_rmsnorm")
+                             _ptr(weight), _ptr(rows), float(eps), n, H, int(groups), _stream()), "le_rmsnorm")
 
 
 def rope_kv_write(qkv, k_cache, v_cache, cos_sin, positions, request_of_token, block_table, num_heads, num_kv_heads,
@@ -431,19 +549,22 @@ def linear_for_residual(a: torch.Tensor, w: torch.Tensor, workspace, key: str, s
     return out
 
 
-def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, workspace, status=None) -> None:
-    """out = silu(a @ w_gate^T) * (a @ w_up^T), w_gate_up = [gate rows; up rows].
-    bfloat16: one kernel of the package (weight-streaming for few rows, tcgen05
-    for many) with the activation in its epilogue."""
-    if skinny_applies(a, w_gate_up):
-        gemm_skinny(out, a, w_gate_up, gated=True)
-        return
-    if tc_applies(a, w_gate_up):
-        gemm_tc(out, a, w_gate_up, gated=True, status=status)
-        return
+def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, workspace, status=None,
+                 activation=(GLU_SILU, 1.0, 0.0)) -> None:
+    """out = act(a @ w_gate^T, a @ w_up^T), w_gate_up = [gate rows; up rows];
+    ``activation``: (kind, slope, limit) as glu() takes them, silu(g) * u by
+    default.  bfloat16: one kernel of the package (weight-streaming for few
+    rows, tcgen05 for many) with the activation in its epilogue."""
+    if activation[0] == GLU_SILU:
+        if skinny_applies(a, w_gate_up):
+            gemm_skinny(out, a, w_gate_up, gated=True)
+            return
+        if tc_applies(a, w_gate_up):
+            gemm_tc(out, a, w_gate_up, gated=True, status=status)
+            return
     gu = workspace.get("gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(gu, a, w_gate_up, status)
-    swiglu(out, gu)
+    glu(out, gu, *activation)
 
 
 def linear(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, status=None) -> None:
@@ -489,8 +610,26 @@ def gemm_bf16_f32out(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> Non
         gemm_simt(out, a, w)
 
 
+def reach_code(window: int | None = None, chunk: int | None = None) -> int:
+    """Which keys a query sees besides none after itself, as the one integer
+    the attention kernels take: 0 every key, w > 0 the last w keys, -c < 0 the
+    keys of its own chunk of c positions (chunks counted from position 0)."""
+    if window and chunk:
+        raise ValueError("a mixer's keys are visible through a window or chunk by chunk, not both")
+    return int(window) if window else (-int(chunk) if chunk else 0)
+
+
+def _head_scale(head_scale, num_heads):
+    if head_scale is not None:
+        assert head_scale.dtype == torch.float32 and head_scale.is_contiguous() and head_scale.numel() == num_heads
+        _need_cuda(head_scale)
+    return _ptr(head_scale)
+
+
 def attention_generic(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
-                      num_tiles, num_heads, num_kv_heads, head_dim, page_size, window, scale, status) -> None:
+                      num_tiles, num_heads, num_kv_heads, head_dim, page_size, reach, scale, status, head_scale=None) -> None:
+    """``reach``: see reach_code.  ``head_scale`` (float32 [num_heads] or None):
+    one more factor per query head on its scores."""
     _need_cuda(out, q, k_cache, v_cache, block_table)
     lib = attention_lib(head_dim)
     assert out.is_contiguous() and out.shape[1] == num_heads * head_dim
@@ -498,8 +637,8 @@ def attention_generic(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx
     _check(lib.le_attention_generic(_ptr(out), out.stride(0), _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache),
                                     dtype_code(out.dtype), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
                                     _ptr(ctx_before), _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads,
-                                    num_kv_heads, page_size, k_cache.shape[0], int(window or 0), float(scale),
-                                    _ptr(status), _stream()), "le_attention_generic", lib)
+                                    num_kv_heads, page_size, k_cache.shape[0], int(reach or 0), float(scale),
+                                    _head_scale(head_scale, num_heads), _ptr(status), _stream()), "le_attention_generic", lib)
 
 
 def attention_mma_available(head_dim: int) -> bool:
@@ -509,7 +648,8 @@ def attention_mma_available(head_dim: int) -> bool:
 
 
 def attention_prefill_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
-                           num_tiles, num_heads, num_kv_heads, head_dim, page_size, window, scale, status) -> None:
+                           num_tiles, num_heads, num_kv_heads, head_dim, page_size, reach, scale, status,
+                           head_scale=None) -> None:
     """Tensor-core attention for requests that bring several tokens; the tiles
     list 128 query tokens each."""
     _need_cuda(out, q, k_cache, v_cache, block_table)
@@ -519,8 +659,9 @@ def attention_prefill_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q
     _check(lib.le_attention_prefill_bf16(_ptr(out), out.stride(0), _ptr(q), q_stride, _ptr(k_cache), _ptr(v_cache),
                                          _ptr(block_table), block_table.shape[1], _ptr(cu_q), _ptr(ctx_before),
                                          _ptr(tile_request), _ptr(tile_q0), num_tiles, num_heads, num_kv_heads,
-                                         page_size, k_cache.shape[0], int(window or 0), float(scale), _ptr(status),
-                                         _stream()), "le_attention_prefill_bf16", lib)
+                                         page_size, k_cache.shape[0], int(reach or 0), float(scale),
+                                         _head_scale(head_scale, num_heads), _ptr(status), _stream()),
+           "le_attention_prefill_bf16", lib)
 
 
 def attention_tc_available(head_dim: int, page_size: int) -> bool:
@@ -529,10 +670,12 @@ def attention_tc_available(head_dim: int, page_size: int) -> bool:
 
 
 def attention_prefill_tc_bf16(out, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, tile_request, tile_q0,
-                              num_tiles, num_heads, num_kv_heads, head_dim, page_size, window, scale, status) -> None:
+                              num_tiles, num_heads, num_kv_heads, head_dim, page_size, reach, scale, status,
+                              head_scale=None) -> None:
     """tcgen05 / TMA attention for requests that bring several tokens (head
     sizes 64 and 128, pages of 8..128 keys); the tiles list 128 query tokens
-    each.  ``q`` is the [T, width] buffer whose rows start with the query heads."""
+    each.  ``q`` is the [T, width] buffer whose rows start with the query heads.
+    ``head_scale`` must be positive here (the kernel folds it into the exponent's scale)."""
     _need_cuda(out, q, k_cache, v_cache, block_table)
     lib = attention_lib(head_dim)
     assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape[1] == num_heads * head_dim
@@ -541,8 +684,9 @@ def attention_prefill_tc_bf16(out, q, q_stride, k_cache, v_cache, block_table, c
     _check(lib.le_attention_prefill_tc_bf16(_ptr(out), out.stride(0), _ptr(q), q_stride, q.shape[0], q.shape[1],
                                             _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
                                             _ptr(cu_q), _ptr(ctx_before), _ptr(tile_request), _ptr(tile_q0), num_tiles,
-                                            num_heads, num_kv_heads, page_size, k_cache.shape[0], int(window or 0),
-                                            float(scale), _ptr(status), _stream()), "le_attention_prefill_tc_bf16", lib)
+                                            num_heads, num_kv_heads, page_size, k_cache.shape[0], int(reach or 0),
+                                            float(scale), _head_scale(head_scale, num_heads), _ptr(status), _stream()),
+           "le_attention_prefill_tc_bf16", lib)
 
 
 def attention_decode_scratch_floats(head_dim: int, num_requests: int, num_heads: int, num_splits: int) -> int:
@@ -572,8 +716,8 @@ def attention_decode_resident_blocks(head_dim: int, num_splits: int, small: bool
 
 
 def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_table, cu_q, ctx_before, requests,
-                          num_requests, num_heads, num_kv_heads, head_dim, page_size, window, scale, num_splits,
-                          status, small_form=None) -> None:
+                          num_requests, num_heads, num_kv_heads, head_dim, page_size, reach, scale, num_splits,
+                          status, small_form=None, head_scale=None) -> None:
     """Split-key tensor-core attention for requests that bring one token.
     ``scratch``: float32, attention_decode_scratch_floats(...) elements.
     ``small_form``: None lets the launcher choose between the kernel's usual
@@ -590,8 +734,9 @@ def attention_decode_bf16(out, scratch, q, q_stride, k_cache, v_cache, block_tab
     _check(lib.le_attention_decode_bf16_form(_ptr(out), out.stride(0), _ptr(scratch), _ptr(q), q_stride, _ptr(k_cache),
                                              _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(cu_q),
                                              _ptr(ctx_before), _ptr(requests), num_requests, num_heads, num_kv_heads,
-                                             page_size, k_cache.shape[0], int(window or 0), float(scale), num_splits,
-                                             form, _ptr(status), _stream()), "le_attention_decode_bf16", lib,
+                                             page_size, k_cache.shape[0], int(reach or 0), float(scale),
+                                             _head_scale(head_scale, num_heads), num_splits, form, _ptr(status), _stream()),
+           "le_attention_decode_bf16", lib,
            launches=2 if num_splits > 1 else 1)       # the attention kernel and the merge
 
 

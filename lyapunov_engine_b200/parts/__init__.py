@@ -1,5 +1,7 @@
-from . import attention, base, block, embedding, feedforward, norm, rope  # noqa: F401  (registers the kinds)
-from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, FeedForward,
+from . import (attention, base, block, embedding, feedforward, latent_attention, norm, rope,  # noqa: F401  (registers the kinds)
+               short_conv)
+from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INPUT_FILTERS, MIXERS, NORMS, POSITION_ENCODINGS, Block, FeedForward,
+                   InputFilter, register_input_filter,
                    KVNeed, LayerSpec, Mixer, ModelSpec, Norm, Part, PartSpec, PositionEncoding, ResidualStream,
                    RunSpec, StateNeed, TensorDecl, register_block, register_embedding, register_feed_forward,
                    register_head, register_mixer, register_norm, register_position_encoding)

@@ -18,6 +18,7 @@ import torch
 
 from .. import ops
 
+MAX_HEAD_DIM = 512              # of the FP32-pipe kernel; the tensor-core kernels end at 128
 GENERIC_TILE = 16
 PREFILL_TILE = 128
 DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
@@ -112,7 +113,12 @@ def decode_splits(num_requests: int, num_heads: int, num_kv_heads: int, context_
                                 small, ops.sm_count())
 
 
-def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int):
+def keys_bound(context_bound: int, reach: int) -> int:
+    """The most keys a decoded token reads: its context, or its window or chunk where that is shorter."""
+    return min(context_bound, abs(reach)) if reach else context_bound
+
+
+def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int, reach: int = 0):
     """The split count (and the kernel's form, where it is not the usual one)
     of a step in which ``fill`` of the one-token requests are real: dummy
     requests finish at once, so the real ones alone fill the waves (9 real
@@ -120,31 +126,39 @@ def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, 
     if not SPLITS_BY_FILL or not ops.attention_mma_available(head_dim):
         return None
     fill = max(1, fill)
-    splits = decode_splits(fill, num_heads, num_kv_heads, context_bound, head_dim)
+    splits = decode_splits(fill, num_heads, num_kv_heads, keys_bound(context_bound, reach), head_dim)
     # (the kernel's form follows the real requests too)
     return (splits, "small") if decode_small_form(fill, num_heads, num_kv_heads, head_dim) else splits
 
 
-def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, window, scale) -> None:
+def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, reach, scale, head_scale=None,
+        head_scale_positive: bool = True) -> None:
+    """``reach``: which keys a query sees (ops.reach_code); ``head_scale``: one
+    more factor per query head on its scores (float32 [num_heads]) or None.
+    The tcgen05 kernel folds that factor into its exponent's scale and so takes
+    positive factors only; the others apply it to the scores themselves."""
     table = ctx.block_tables[kv.group]
+    window = reach
     if out.dtype == torch.bfloat16 and ops.attention_mma_available(head_dim):
         req, q0, n_tiles, n_multi = ctx.tiles[PREFILL_TILE]
         if n_multi:
-            prefill = (ops.attention_prefill_tc_bf16 if USE_TC_ATTENTION and ops.attention_tc_available(head_dim, kv.page_size)
+            prefill = (ops.attention_prefill_tc_bf16
+                       if USE_TC_ATTENTION and head_scale_positive and ops.attention_tc_available(head_dim, kv.page_size)
                        else ops.attention_prefill_bf16)
             prefill(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_multi, num_heads,
-                    num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status)
+                    num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status, head_scale=head_scale)
         if ctx.num_decode:
             real = min(ctx.decode_fill, ctx.num_decode) if SPLITS_BY_FILL else 0     # dummy requests finish at once
-            splits = decode_splits(real or ctx.num_decode, num_heads, num_kv_heads, ctx.context_bound, head_dim)
+            splits = decode_splits(real or ctx.num_decode, num_heads, num_kv_heads, keys_bound(ctx.context_bound, reach),
+                                   head_dim)
             small = decode_small_form(real or ctx.num_decode, num_heads, num_kv_heads, head_dim)
             floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)
             scratch = ctx.workspace.get("attention_scratch", (floats,), torch.float32) if floats else None
             requests = None if ctx.num_decode == ctx.num_requests else ctx.decode_requests
             ops.attention_decode_bf16(out, scratch, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before,
                                       requests, ctx.num_decode, num_heads, num_kv_heads, head_dim, kv.page_size,
-                                      window, scale, splits, ctx.status, small_form=small)
+                                      window, scale, splits, ctx.status, small_form=small, head_scale=head_scale)
         return
     req, q0, n_tiles, _ = ctx.tiles[GENERIC_TILE]
     ops.attention_generic(out, qkv, qkv.stride(0), kv.k, kv.v, table, ctx.cu_q, ctx.ctx_before, req, q0, n_tiles,
-                          num_heads, num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status)
+                          num_heads, num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status, head_scale=head_scale)

@@ -33,6 +33,10 @@ Interfaces (all tensors are CUDA tensors; T tokens in the step, H width):
     mixers keep state are never padded with dummy tokens behind a request's
     own.  ``tile_sizes()`` names the query-tile sizes its kernels want listed
     in the step's integers (``ctx.tiles``).
+``InputFilter``
+    ``forward(x, ctx, state) -> x'``: what a block puts between a norm and the
+    sub-layer that reads it (a short convolution over time, say); it may keep
+    per-request state of its own (``state_need()``), which the block hands it.
 ``FeedForward``
     ``forward(x, ctx) -> y``.
 ``Block``
@@ -98,21 +102,30 @@ class TensorDecl:
     in: "matrix" in the engine's compute type (bfloat16 or float32); "vector"
     (norm weights and the like) always 32-bit, so one stored in 32 bits stays
     exactly so; "int_table" as int32.  ``init`` is how random weights fill it:
-    "normal", "ones", "ones_jitter" or "zeros".  ``alias_of`` names the tensor
-    that stands in when the checkpoint has none of this name (a tied head)."""
+    "normal", "ones", "ones_jitter", "zeros" or "taps" (small numbers around
+    zero).  ``alias_of`` names the tensor
+    that stands in when the checkpoint has none of this name (a tied head).
+    ``std_scale``: random matrices are N(0, std * std_scale)."""
     name: str
     shape: tuple[int, ...]
     role: str = "matrix"
     init: str = "normal"
     alias_of: str | None = None
+    std_scale: float = 1.0
 
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values in pages: ``window`` None keeps every key."""
+    """Keys and values in pages.  ``window`` w: a query reads the last w keys
+    only; ``chunk`` c: a query reads the keys of its own chunk of c positions
+    only (chunks counted from position 0); neither: every key is kept.
+    ``values`` False: one pool serves as keys and as values (a mixer that
+    attends over one latent vector per token)."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    chunk: int | None = None
+    values: bool = True
 
 
 @dataclass(frozen=True)
@@ -167,6 +180,17 @@ class Mixer(Part):
         raise NotImplementedError
 
 
+class InputFilter(Part):
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def tile_sizes(self) -> list[int]:
+        return []
+
+    def forward(self, x, ctx, state):
+        raise NotImplementedError
+
+
 class FeedForward(Part):
     def forward(self, x, ctx):
         raise NotImplementedError
@@ -174,6 +198,15 @@ class FeedForward(Part):
 
 class Block(Part):
     mixer: Mixer
+
+    def extra_state_needs(self) -> dict[str, StateNeed]:
+        """Per-request state that parts of the block other than the mixer keep,
+        by a name of the block's choosing; ``cache.extra[name]`` holds each
+        buffer when the block runs (rows by state slot, as the mixer's)."""
+        return {}
+
+    def tile_sizes(self) -> list[int]:
+        return list(self.mixer.tile_sizes())
 
     def forward(self, stream, ctx, cache) -> None:
         raise NotImplementedError
@@ -218,6 +251,7 @@ NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
+INPUT_FILTERS = Registry("input filter")
 BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
@@ -226,6 +260,7 @@ register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
+register_input_filter = INPUT_FILTERS.register
 register_block = BLOCKS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register

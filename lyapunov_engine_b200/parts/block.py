@@ -6,23 +6,38 @@ residual stream.
     h = h + mixer(norm1(h));  h = h + feed_forward(norm2(h))
 The additions happen inside the following norm's kernel, in 32 bits: a block
 leaves its feed-forward output ``pending`` and the next norm (of the next
-block, or the final one) adds it.
+block, or the final one) adds it.  Two options: ``mixer_input``, an input
+filter between the first norm and the mixer (h = filter(norm1(h)) is what the
+mixer reads), and a block without a feed-forward (``feed_forward`` None: only
+the first line above).
 """
 from __future__ import annotations
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, PartSpec, register_block
+from .base import BLOCKS, FEED_FORWARDS, INPUT_FILTERS, MIXERS, NORMS, Block, PartSpec, register_block
 
 
 @register_block("prenorm")
 class PreNormBlock(Block):
-    def __init__(self, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, feed_forward_norm: PartSpec):
+    def __init__(self, mixer: PartSpec, feed_forward: PartSpec | None, mixer_norm: PartSpec,
+                 feed_forward_norm: PartSpec | None, mixer_input: PartSpec | None = None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a block has a feed-forward and its norm, or neither")
         self.mixer = MIXERS.build(mixer)
-        self.feed_forward = FEED_FORWARDS.build(feed_forward)
+        self.feed_forward = FEED_FORWARDS.build(feed_forward) if feed_forward is not None else None
         self.mixer_norm = NORMS.build(mixer_norm)
-        self.feed_forward_norm = NORMS.build(feed_forward_norm)
+        self.feed_forward_norm = NORMS.build(feed_forward_norm) if feed_forward_norm is not None else None
+        self.mixer_input = INPUT_FILTERS.build(mixer_input) if mixer_input is not None else None
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer_input, self.mixer, self.feed_forward_norm, self.feed_forward)
+                if p is not None]
+
+    def extra_state_needs(self):
+        need = self.mixer_input.state_need() if self.mixer_input is not None else None
+        return {"mixer_input": need} if need is not None else {}
+
+    def tile_sizes(self):
+        return list(self.mixer.tile_sizes()) + (self.mixer_input.tile_sizes() if self.mixer_input is not None else [])
 
     def tensors(self):
         return [d for p in self.parts() for d in p.tensors()]
@@ -33,6 +48,11 @@ class PreNormBlock(Block):
 
     def forward(self, stream, ctx, cache) -> None:
         n = self.mixer_norm.apply(stream.resid, stream.pending, workspace=ctx.workspace)
+        if self.mixer_input is not None:
+            n = self.mixer_input.forward(n, ctx, (cache.extra or {}).get("mixer_input"))
         a = self.mixer.forward(n, ctx, cache)
+        if self.feed_forward is None:
+            stream.pending = a
+            return
         n = self.feed_forward_norm.apply(stream.resid, a, workspace=ctx.workspace)
         stream.pending = self.feed_forward.forward(n, ctx)

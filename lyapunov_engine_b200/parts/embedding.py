@@ -35,6 +35,32 @@ class TokenEmbedding(Part):
         return resid
 
 
+@register_embedding("token_embedding_sinusoid")
+class SinusoidTokenEmbedding(TokenEmbedding):
+    """h0[t] = E[id_t] + s(p_t) with the fixed position vector
+    s(p)[2i] = sin(p * base^(-2i/W)), s(p)[2i + 1] = cos(p * base^(-2i/W)),
+    W the width and p the token's position in its request.  The rates are
+    made once in 64 bits and kept as float32; angle, sine and cosine are
+    32-bit, computed in the embedding kernel for the step's own positions (no
+    table, so no limit on positions)."""
+
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, base: float = 10000.0):
+        super().__init__(vocab_size, hidden_size, weight_name)
+        self.base = float(base)
+        self.rates = None
+
+    def bind(self, get, runtime):
+        super().bind(get, runtime)
+        i = torch.arange(0, self.hidden_size, 2, dtype=torch.float64)
+        rates = torch.pow(torch.tensor(self.base, dtype=torch.float64), -i / self.hidden_size)
+        self.rates = rates.to(torch.float32).to(runtime.device).contiguous()
+
+    def forward(self, ctx):
+        resid = ctx.workspace.get("resid", (ctx.num_tokens, self.hidden_size), torch.float32)
+        ops.embed_sinusoid(resid, self.weight, ctx.token_ids, ctx.positions, self.rates, ctx.status)
+        return resid
+
+
 @register_head("linear_head")
 class LinearHead(Part):
     def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, tied_to: str | None = None):

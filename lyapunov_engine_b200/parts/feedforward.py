@@ -1,4 +1,8 @@
-"""Gated feed-forward (SwiGLU): down(silu(gate(x)) * up(x)).
+"""Gated feed-forward: down(act(gate(x), up(x))).
+
+"gated_silu" (SwiGLU): act(g, u) = silu(g) * u.  "gated_clamped": with a limit
+L and a slope a, g' = min(g, L), u' = clamp(u, -L, L), act = g' * sigmoid(a g')
+* (u' + 1).
 
 Gate and up are one projection [2 I, H], gate rows first, as the reference
 fuses them at load (python/lyapunov_engine/models/weight_loader.py:155-163;
@@ -15,6 +19,8 @@ from .base import FeedForward, TensorDecl, register_feed_forward
 
 @register_feed_forward("gated_silu")
 class GatedFeedForward(FeedForward):
+    activation = (ops.GLU_SILU, 1.0, 0.0)      # (kind, slope, limit) as the kernels take them
+
     def __init__(self, hidden_size: int, intermediate_size: int, gate_name: str, up_name: str, down_name: str):
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.names = (gate_name, up_name, down_name)
@@ -37,5 +43,15 @@ class GatedFeedForward(FeedForward):
         T = x.shape[0]
         ws = ctx.workspace
         act = ws.get("ffn_act", (T, self.intermediate_size), rt.dtype)
-        ops.gated_linear(act, x, self.w_gate_up, ws, ctx.status)
+        ops.gated_linear(act, x, self.w_gate_up, ws, ctx.status, self.activation)
         return ops.linear_for_residual(act, self.w_down, ws, "ffn_out", ctx.status)
+
+
+@register_feed_forward("gated_clamped")
+class ClampedGatedFeedForward(GatedFeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int, gate_name: str, up_name: str, down_name: str,
+                 limit: float, slope: float = 1.702):
+        super().__init__(hidden_size, intermediate_size, gate_name, up_name, down_name)
+        if not limit > 0:
+            raise ValueError(f"the clamped activation needs a positive limit, got {limit}")
+        self.activation = (ops.GLU_CLAMPED, float(slope), float(limit))

@@ -12,8 +12,14 @@ from .base import Norm, TensorDecl, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    def __init__(self, hidden_size: int, eps: float, weight_name: str):
+    """``groups`` > 1: the row is cut into that many equal consecutive parts,
+    each divided by its own sqrt(mean(part^2) + eps), before the weight."""
+
+    def __init__(self, hidden_size: int, eps: float, weight_name: str, groups: int = 1):
         self.hidden_size = int(hidden_size)
+        self.groups = int(groups)
+        if self.groups < 1 or self.hidden_size % self.groups:
+            raise ValueError(f"a norm over {hidden_size} values cannot be cut into {groups} equal parts")
         self.eps = float(eps)
         self.weight_name = weight_name
         self.weight = None
@@ -30,5 +36,5 @@ class RMSNorm(Norm):
         n = resid.shape[0] if rows is None else rows.shape[0]
         ws = workspace or self.runtime.workspace
         out = ws.get(key, (n, self.hidden_size), self.runtime.dtype)
-        ops.rmsnorm(out, resid, delta, self.weight, self.eps, rows)
+        ops.rmsnorm(out, resid, delta, self.weight, self.eps, rows, groups=self.groups)
         return out

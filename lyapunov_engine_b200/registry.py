@@ -1,6 +1,7 @@
 """One registry from an architecture's name to what builds its model.
 
-``architectures[0]`` of config.json (else ``model_type``) selects a function
+``architectures[0]`` of config.json (else ``model_type``, else the string
+``architecture``) selects a function
 that turns the raw config.json into a ``ModelSpec``.  The reference has no
 registry: its command line calls the Llama loader directly
 (python/lyapunov_engine/entrypoints/cli.py:20).
@@ -29,7 +30,9 @@ def architecture_name(raw_config: dict) -> str:
         return archs[0]
     if raw_config.get("model_type"):
         return raw_config["model_type"]
-    raise ConfigError("config.json names no architecture (neither 'architectures' nor 'model_type')")
+    if isinstance(raw_config.get("architecture"), str):
+        return raw_config["architecture"]
+    raise ConfigError("config.json names no architecture (none of 'architectures', 'model_type', 'architecture')")
 
 
 def known_architectures() -> list[str]:
@@ -45,9 +48,11 @@ def spec_for(raw_config: dict) -> ModelSpec:
 
 def _register_builtin() -> None:
     from .models.llama import llama_spec
+    from .models.sulepel import sulepel_spec
 
     register_architecture("LlamaForCausalLM", llama_spec)
     register_architecture("llama", llama_spec)
+    register_architecture("Sulepel", sulepel_spec)
 
 
 _register_builtin()

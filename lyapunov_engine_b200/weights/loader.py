@@ -124,7 +124,9 @@ class RandomWeights:
         if d.role == "int_table":
             return torch.zeros(d.shape, dtype=torch.int32, device=self.device)
         if d.init == "normal":
-            t = torch.randn(d.shape, generator=self.generator, device=self.device, dtype=torch.float32) * self.std
+            t = torch.randn(d.shape, generator=self.generator, device=self.device, dtype=torch.float32) * (self.std * d.std_scale)
+        elif d.init == "taps":
+            t = torch.randn(d.shape, generator=self.generator, device=self.device, dtype=torch.float32) * 0.25
         elif d.init in ("ones", "ones_jitter"):
             t = torch.ones(d.shape, device=self.device, dtype=torch.float32)
             if d.init == "ones_jitter" and self.norm_jitter:
