@@ -162,6 +162,24 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Gated activations of a fused gate/up product, act(g, u), in 32 bits:
+//   kind 0: silu(g) * u
+//   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(slope * g') * (u' + 1)
+struct GatedActivation {
+  int kind = 0;
+  float slope = 1.0f;
+  float limit = 0.0f;
+};
+template <bool FAST_EXP = false>
+__device__ __forceinline__ float gated_activation(float g, float u, const GatedActivation &a) {
+  if (a.kind == 1) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit) + 1.0f;
+    return g / (1.0f + (FAST_EXP ? __expf(-a.slope * g) : expf(-a.slope * g))) * u;
+  }
+  return g / (1.0f + (FAST_EXP ? __expf(-g) : expf(-g))) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

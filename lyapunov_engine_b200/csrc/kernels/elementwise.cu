@@ -53,26 +53,16 @@ __global__ void embed_sinusoid_kernel(float *__restrict__ out, const T *__restri
   }
 }
 
-// Gated activations of a fused gate/up product, in 32-bit, rounded once.
-//   kind 0: silu(g) * u
-//   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(alpha * g') * (u' + 1)
-__device__ __forceinline__ float glu_value(float g, float u, int kind, float alpha, float limit) {
-  if (kind == 0) return g / (1.0f + expf(-g)) * u;
-  g = fminf(g, limit);
-  u = fminf(fmaxf(u, -limit), limit);
-  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
-}
-
+// out[t, i] = act(gu[t, i], gu[t, I + i]) (le::gated_activation), in 32-bit, rounded once.
 template <typename T>
-__global__ void glu_kernel(T *__restrict__ out, const T *__restrict__ gu, int64_t total, int inter, int kind, float alpha,
-                           float limit) {
+__global__ void glu_kernel(T *__restrict__ out, const T *__restrict__ gu, int64_t total, int inter, le::GatedActivation act) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const int64_t t = idx / inter;
   const int i = static_cast<int>(idx - t * inter);
   const float g = le::to_f32(gu[t * 2 * inter + i]);
   const float u = le::to_f32(gu[t * 2 * inter + inter + i]);
-  out[idx] = le::from_f32<T>(glu_value(g, u, kind, alpha, limit));
+  out[idx] = le::from_f32<T>(le::gated_activation(g, u, act));
 }
 
 // x[t, h, :] *= sigmoid(gate[t, h]): one number per token and head scales that
@@ -179,7 +169,7 @@ LE_API int le_embed_sinusoid(float *out, const void *table, int table_dtype, con
                                               static_cast<const T *>(table), ids, positions, rates, hidden, vocab, status));
 }
 
-// out[T, I] from gate_up[T, 2 I] (gate columns first) by the activation `kind` (see glu_value).
+// out[T, I] from gate_up[T, 2 I] (gate columns first) by the activation `kind` (see le::GatedActivation).
 LE_API int le_glu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, int kind, float alpha, float limit,
                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
@@ -190,7 +180,7 @@ LE_API int le_glu(void *out, const void *gate_up, int dtype, int num_tokens, int
   if (blocks > 2147483647LL) return le::invalid("le_glu: %lld elements are too many for one launch", (long long)total);
   LE_DISPATCH_DTYPE(dtype, T,
                     glu_kernel<T><<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
-                        static_cast<T *>(out), static_cast<const T *>(gate_up), total, inter, kind, alpha, limit));
+                        static_cast<T *>(out), static_cast<const T *>(gate_up), total, inter, le::GatedActivation{kind, alpha, limit}));
   return le::launched();
 }
 

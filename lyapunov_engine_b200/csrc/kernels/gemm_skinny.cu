@@ -77,7 +77,7 @@ template <int MT, int RG, bool GATED, typename TO, int BK, int STAGES, bool ROTA
 __global__ void __launch_bounds__(THREADS)
 gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 *__restrict__ w, int M, int N, int K,
                    int64_t ldx, int64_t ldw, int64_t ldo, int k_per_split, int64_t split_stride, int early_successor,
-                   RotaryArgs rotary) {
+                   RotaryArgs rotary, le::GatedActivation act) {
   static_assert(!ROTARY || RG == 1, "the rotary form takes one group of rows a block");
   constexpr int WSETS = GATED ? 2 : 1;
   constexpr int ROWS = BN * RG;                    // weight rows per set and block
@@ -309,7 +309,7 @@ gemm_skinny_kernel(TO *__restrict__ out, const bf16 *__restrict__ x, const bf16 
       const int row = m * 8 + 2 * t + (e & 1);
       if (n < n_out && row < M) {
         float x = v[0];
-        if constexpr (GATED) x = x / (1.0f + expf(-x)) * v[WSETS - 1];
+        if constexpr (GATED) x = le::gated_activation(x, v[WSETS - 1], act);
         dst[row * ldo + n] = le::from_f32<TO>(x);
       }
     }
@@ -363,7 +363,7 @@ struct Form {
     return n;
   }
   static int go(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
-                int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary) {
+                int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary, const le::GatedActivation &act) {
     if (resident() <= 0) return le::invalid("le_gemm_skinny: cannot get %zu bytes of shared memory", smem());
     const int n_out = GATED ? N / 2 : N;
     int k_per_split = (K + splits - 1) / splits;
@@ -373,7 +373,7 @@ struct Form {
     const int early = (early_trigger_mask() & form) && static_cast<int64_t>(grid.x) * grid.y <= resident() ? 1 : 0;
     return le::launch_chained(gemm_skinny_kernel<MT, RG, GATED, TO, BK, STAGES, ROTARY>, grid, dim3(THREADS), smem(), stream,
                               static_cast<TO *>(out), static_cast<const bf16 *>(x), static_cast<const bf16 *>(w), M, N, K, ldx, ldw,
-                              ldo, k_per_split, split_stride, early, rotary);
+                              ldo, k_per_split, split_stride, early, rotary, act);
   }
 };
 
@@ -388,7 +388,8 @@ bool wide_split_k_enabled() {
 
 template <int MT, bool GATED, typename TO, bool ROTARY = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
-           int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary = RotaryArgs{}) {
+           int64_t split_stride, cudaStream_t stream, const RotaryArgs &rotary = RotaryArgs{},
+           const le::GatedActivation &act = le::GatedActivation{}) {
   if constexpr (MT <= 2 || ROTARY) {
     // Few rows leave shared memory for a deeper pipeline: more bytes in flight per block (3 % of a decode step).
     // Not for the gated form: with two weight tiles per stage its 512 blocks no longer fit the GPU all at once.
@@ -403,45 +404,48 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
       // 0.683 -> 0.671.  (Not the gated form: no gain at 9 to 16 tokens, slower below; not the output head's
       // unsplit product: slower up to 8 tokens; 64 rows a block: slower.)
       if (splits > 1 && wide_split_k_enabled())
-        return Form<MT, 2, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+        return Form<MT, 2, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary, act);
     }
-    return Form<MT, 1, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+    return Form<MT, 1, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary, act);
   } else {
     // 17 to 64 tokens: a block takes 64 weight rows where K is split (many blocks anyway), else 32 (or 32 gate and
     // 32 up rows), with as many stages as leave two blocks a multiprocessor
     constexpr int STAGES = MT <= 4 ? 4 : 3;
     if constexpr (!GATED) {
       if (splits > 1)
-        return Form<MT, 4, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+        return Form<MT, 4, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary, act);
     }
-    return Form<MT, 2, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary);
+    return Form<MT, 2, GATED, TO, ROTARY, STAGES>::go(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, rotary, act);
   }
 }
 
 template <bool GATED, typename TO>
 int dispatch_m(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int splits,
-               int64_t split_stride, cudaStream_t stream) {
-  if (M <= 8) return launch<1, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);
-  if (M <= 16) return launch<2, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);
-  if (M <= 32) return launch<4, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);
-  return launch<8, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);
+               int64_t split_stride, cudaStream_t stream, const le::GatedActivation &act = le::GatedActivation{}) {
+  if (M <= 8) return launch<1, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, RotaryArgs{}, act);
+  if (M <= 16) return launch<2, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, RotaryArgs{}, act);
+  if (M <= 32) return launch<4, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, RotaryArgs{}, act);
+  return launch<8, GATED, TO>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream, RotaryArgs{}, act);
 }
 
 }  // namespace
 
 // gated = 0: out[M, N] (out_dtype bfloat16 or float32) = x W^T; with splits > 1
 // out is float32 [splits, M, N] (split s at out + s * split_stride elements).
-// gated = 1: W is [N = 2 I, K], out is bfloat16 [M, I]; splits must be 1.
+// gated = 1: W is [N = 2 I, K], out is bfloat16 [M, I] = act(x Wg^T, x Wu^T) with the activation
+// (act_kind, act_slope, act_limit) of le::GatedActivation (0: silu(g) * u); splits must be 1.
 // Needs M <= 64, K a multiple of 8, 16-byte aligned rows of x and W.
 LE_API int le_gemm_skinny_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx,
-                               int64_t ldw, int64_t ldo, int splits, int64_t split_stride, int gated, cudaStream_t stream) {
+                               int64_t ldw, int64_t ldo, int splits, int64_t split_stride, int gated, int act_kind,
+                               float act_slope, float act_limit, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (M > 64) return le::invalid("le_gemm_skinny_bf16: at most 64 rows, got %d", M);
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_skinny_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
   if (splits < 1 || splits > 65535) return le::invalid("le_gemm_skinny_bf16: %d splits", splits);
   if (gated) {
     if (splits != 1 || out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_skinny_bf16: the gated form has one split, bfloat16 output and an even N");
-    return dispatch_m<true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream);
+    if (act_kind != 0 && act_kind != 1) return le::invalid("le_gemm_skinny_bf16: unknown activation %d", act_kind);
+    return dispatch_m<true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, le::GatedActivation{act_kind, act_slope, act_limit});
   }
   if (splits > 1 && out_dtype != LE_F32) return le::invalid("le_gemm_skinny_bf16: partial sums of a split K are float32");
   if (out_dtype == LE_F32) return dispatch_m<false, float>(out, x, w, M, N, K, ldx, ldw, ldo, splits, split_stride, stream);

@@ -112,7 +112,8 @@ __device__ __forceinline__ void tile_position(int tile, int tiles_m, int tiles_n
 template <int BN, bool GATED, typename TO, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO *__restrict__ out,
-               int M, int N, int K, int64_t ldo, int up_row_offset, int tiles_m, int tiles_n, int *__restrict__ status) {
+               int M, int N, int K, int64_t ldo, int up_row_offset, int tiles_m, int tiles_n, int *__restrict__ status,
+               le::GatedActivation act) {
   static_assert(!PAIR || BN == 256, "a pair of blocks computes 256 x 256 tiles");
   constexpr int B_ROWS = PAIR ? BN / 2 : BN;         // rows of W in this block's stage
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -269,7 +270,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               f[i] = __uint_as_float(v[j + i]);
-              if (GATED) f[i] = f[i] / (1.0f + __expf(-f[i])) * __uint_as_float(u[j + i]);
+              if (GATED) f[i] = le::gated_activation<true>(f[i], __uint_as_float(u[j + i]), act);
             }
             if (col + 8 <= n_limit && (reinterpret_cast<uintptr_t>(dst + col) & 15) == 0) {
               if constexpr (sizeof(TO) == 2) {
@@ -330,7 +331,7 @@ bool pairs_enabled() {
 
 template <int BN, bool GATED, typename TO, bool PAIR = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int *status,
-           cudaStream_t stream) {
+           cudaStream_t stream, const le::GatedActivation &act = le::GatedActivation{}) {
   // 192 KB of stages either way: one persistent block per SM
   constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : 6);
   constexpr int W_ROWS = PAIR ? BN / 2 : BN;             // rows of W per block and stage
@@ -382,7 +383,7 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
     config.gridDim = dim3(static_cast<int>(tiles < sms ? tiles : sms));
   }
   e = cudaLaunchKernelEx(&config, kernel, map_a, map_b, static_cast<TO *>(out), M, N, K, ldo, GATED ? N / 2 : 0, tiles_m, tiles_n,
-                         status);
+                         status, act);
   if (e != cudaSuccess) return le::invalid("le_gemm_tc_bf16: launch failed: %s", cudaGetErrorString(e));
   return le::launched();
 }
@@ -391,11 +392,15 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
 
 // gated = 0: out[M, N] (bfloat16 or float32) = x W^T.  gated = 1: W is
 // [N = 2 I, K] (gate rows, then up rows), out is bfloat16 [M, I] =
-// silu(x Wg^T) * (x Wu^T).  Needs K and the leading dimensions of x and W to
+// act(x Wg^T, x Wu^T) with the activation (act_kind, act_slope, act_limit) of
+// le::GatedActivation (0: silu(g) * u).  Needs K and the leading dimensions of x and W to
 // be multiples of 8 and their base addresses 16-byte aligned (TMA).
 LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw,
-                           int64_t ldo, int gated, int *status, cudaStream_t stream) {
+                           int64_t ldo, int gated, int act_kind, float act_slope, float act_limit, int *status,
+                           cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (act_kind != 0 && act_kind != 1) return le::invalid("le_gemm_tc_bf16: unknown activation %d", act_kind);
+  const le::GatedActivation act{act_kind, act_slope, act_limit};
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_tc_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return le::invalid("le_gemm_tc_bf16: x and W must be 16-byte aligned");
   // pairs of SMs on 256 x 256 tiles where those give at least half of the pairs a tile and the second block of a
@@ -405,12 +410,12 @@ LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *
   const bool pair = pairs_enabled() && M > BM && pair_tiles >= 37;
   if (gated) {
     if (out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_tc_bf16: the gated form has bfloat16 output and an even N");
-    if (pair) return launch<256, true, bf16, true>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
+    if (pair) return launch<256, true, bf16, true>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream, act);
     // a tile's 256 rows of W are 128 gate and 128 up rows; narrower tiles only where the wide ones would leave
     // more than half of the SMs without one (few rows of x: the product is bound by fetching W)
     const int64_t gated_tiles = static_cast<int64_t>((M + BM - 1) / BM) * ((N / 2 + 127) / 128);
-    if (gated_tiles >= 74) return launch<256, true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
-    return launch<128, true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
+    if (gated_tiles >= 74) return launch<256, true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream, act);
+    return launch<128, true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream, act);
   }
   // 128 x 256 tiles: an MMA instruction costs about the same to issue whatever its width, so the wide tile is
   // the faster one (measured on every shape of the model, 2,048 to 8,192 rows) unless it leaves more than half

@@ -83,9 +83,9 @@ _CORE_SIGNATURES = {
     "le_gemm_heads": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                       c_void_p],
     "le_gemm_tc_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
-                        c_void_p, c_void_p],
+                        c_int, c_float, c_float, c_void_p, c_void_p],
     "le_gemm_skinny_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
-                            c_int64, c_int, c_void_p],
+                            c_int64, c_int, c_int, c_float, c_float, c_void_p],
     "le_gemm_skinny_rotary_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                    c_int, c_void_p, c_void_p],
@@ -423,10 +423,12 @@ def skinny_applies(a: torch.Tensor, w: torch.Tensor, rows: int | None = None) ->
             and w.stride(1) == 1 and a.stride(0) % 8 == 0 and w.stride(0) % 8 == 0)
 
 
-def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int = 1, gated: bool = False) -> None:
+def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int = 1, gated: bool = False,
+                activation=(0, 1.0, 0.0)) -> None:
     """The package's weight-streaming product for at most 64 rows (bfloat16
     inputs).  ``splits`` > 1: ``out`` is float32 [splits, M, N] partial sums.
-    ``gated``: ``w`` is [2 I, K] (gate rows, then up rows), out = silu(gate) * up."""
+    ``gated``: ``w`` is [2 I, K] (gate rows, then up rows), out = act(gate, up)
+    with ``activation`` = (kind, slope, limit) as glu() takes them (silu(gate) * up by default)."""
     _need_cuda(out, a, w)
     M, K = a.shape
     N = w.shape[0]
@@ -437,7 +439,8 @@ def gemm_skinny(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, splits: int
         assert out.shape[-2:] == (M, N // 2 if gated else N) and out.stride(-1) == 1
         ldo, stride = out.stride(-2), 0
     _check(core().le_gemm_skinny_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0),
-                                      w.stride(0), ldo, splits, stride, 1 if gated else 0, _stream()),
+                                      w.stride(0), ldo, splits, stride, 1 if gated else 0, int(activation[0]),
+                                      float(activation[1]), float(activation[2]), _stream()),
            "le_gemm_skinny_bf16")
 
 
@@ -476,10 +479,12 @@ def gemm_skinny_rotary(qkv, a, w, k_cache, v_cache, cos_sin, positions, request_
 _tc_status = {}
 
 
-def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, status=None) -> None:
+def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = False, status=None,
+            activation=(0, 1.0, 0.0)) -> None:
     """The package's tcgen05 / TMA product for many rows (bfloat16 inputs):
-    out = a @ w^T (bfloat16 or float32), or with ``gated`` out = silu(a Wg^T) *
-    (a Wu^T) for w = [Wg; Wu]."""
+    out = a @ w^T (bfloat16 or float32), or with ``gated`` out = act(a Wg^T,
+    a Wu^T) for w = [Wg; Wu], ``activation`` = (kind, slope, limit) as glu()
+    takes them (silu(g) * u by default)."""
     _need_cuda(out, a, w)
     M, K = a.shape
     N = w.shape[0]
@@ -488,7 +493,8 @@ def gemm_tc(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor, gated: bool = F
     if status is None:
         status = tc_status(a.device)
     _check(core().le_gemm_tc_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0),
-                                  out.stride(0), 1 if gated else 0, _ptr(status), _stream()), "le_gemm_tc_bf16")
+                                  out.stride(0), 1 if gated else 0, int(activation[0]), float(activation[1]),
+                                  float(activation[2]), _ptr(status), _stream()), "le_gemm_tc_bf16")
 
 
 def tc_status(device) -> torch.Tensor:
@@ -555,13 +561,12 @@ def gated_linear(out: torch.Tensor, a: torch.Tensor, w_gate_up: torch.Tensor, wo
     ``activation``: (kind, slope, limit) as glu() takes them, silu(g) * u by
     default.  bfloat16: one kernel of the package (weight-streaming for few
     rows, tcgen05 for many) with the activation in its epilogue."""
-    if activation[0] == GLU_SILU:
-        if skinny_applies(a, w_gate_up):
-            gemm_skinny(out, a, w_gate_up, gated=True)
-            return
-        if tc_applies(a, w_gate_up):
-            gemm_tc(out, a, w_gate_up, gated=True, status=status)
-            return
+    if skinny_applies(a, w_gate_up):
+        gemm_skinny(out, a, w_gate_up, gated=True, activation=activation)
+        return
+    if tc_applies(a, w_gate_up):
+        gemm_tc(out, a, w_gate_up, gated=True, status=status, activation=activation)
+        return
     gu = workspace.get("gate_up", (a.shape[0], w_gate_up.shape[0]), a.dtype)
     linear(gu, a, w_gate_up, status)
     glu(out, gu, *activation)

@@ -37,7 +37,8 @@ def parse_args(argv=None):
                    help="tokens that live requests hold at most (each rounded up to a multiple of 64)")
     p.add_argument("--block-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
     p.add_argument("--device", default="cuda:0")
-    p.add_argument("--max-num-seqs", type=int, default=8)
+    p.add_argument("--max-num-seqs", type=int, default=4,
+                   help="requests that are live at any time (state slots; they are used again as requests end)")
     p.add_argument("--no-cuda-graphs", action="store_true")
     return p.parse_args(argv)
 
