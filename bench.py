@@ -146,7 +146,7 @@ def make_rig(cfg, context, max_batch, page):
                                             max_model_len=context + 64))
     runner, manager, sampler = engine.runner, engine.block_manager, engine.sampler
     gen = torch.Generator().manual_seed(0)
-    vocab = cfg["vocab_size"]
+    vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     # Synthetic cache content: timing does not depend on what the pages hold,
     # but a softmax over zeros would be a degenerate case.
     for pools in engine.cache.streams:
@@ -762,6 +762,245 @@ def run_kernels(args):
     return 0
 
 
+# ---------------------------------------------------------------- the Sulepel design beside Llama at equal sizes
+SULEPEL_CHUNK = 2048       # keys a chunked layer's query sees at most
+SULEPEL_LATENT = 128       # latent size (the tensor-core attention kernels end at a head size of 128)
+
+
+def sulepel_config(llama: dict) -> dict:
+    """A Sulepel model with the width, feed-forward size, heads, head size, layer count and vocabulary of the given
+    Llama shapes: three latent-attention layers, then one chunked-attention layer, and so on."""
+    nh, nkv, hd = llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"]
+    mlp = {"kind": "dense", "ff": llama["intermediate_size"], "limit": 7.0}
+    latent = {"type": "latent_attention", "mlp": mlp,
+              "mixer": {"heads": nh, "dim": hd, "vdim": hd, "kv_rank": SULEPEL_LATENT, "scale": hd ** -0.5}}
+    chunked = {"type": "attention", "mlp": mlp,
+               "mixer": {"heads": nh, "kv_heads": nkv, "dim": hd, "vdim": hd, "mask": {"size": SULEPEL_CHUNK}, "scale": hd ** -0.5}}
+    return {"architecture": "Sulepel", "vocab": llama["vocab_size"], "width": llama["hidden_size"],
+            "norm": {"eps": 1e-5, "groups": 4}, "canon": {"taps": 4},
+            "layers": [chunked if i % 4 == 3 else latent for i in range(llama["num_hidden_layers"])]}
+
+
+def sulepel_decode_bytes(cfg, batch, context):
+    """Bytes one decode step of a Sulepel model must read (bfloat16 weights once, the cached latents and the keys and
+    values of the current chunk of every live request)."""
+    W, V = cfg["width"], cfg["vocab"]
+    total = 2 * V * W + 4 * W
+    for layer in cfg["layers"]:
+        m, F = layer["mixer"], layer["mlp"]["ff"]
+        nh, d, e = m["heads"], m["dim"], m["vdim"]
+        total += 2 * 3 * F * W + 4 * (2 + cfg["canon"]["taps"]) * W
+        if layer["type"] == "latent_attention":
+            r = m["kv_rank"]
+            total += 2 * ((nh * d + r + nh) * W + nh * d * r + nh * e * r + W * nh * e) + 2 * batch * context * r
+        else:
+            seen = (context - 1) % m["mask"]["size"] + 1
+            total += 2 * ((nh * d + m["kv_heads"] * (d + e) + nh) * W + W * nh * e) + 2 * batch * seen * m["kv_heads"] * (d + e)
+    return total
+
+
+def sulepel_prefill_flops(cfg, tokens):
+    W, V = cfg["width"], cfg["vocab"]
+    flops = 2 * V * W
+    pairs = tokens * (tokens + 1) // 2
+    for layer in cfg["layers"]:
+        m, F = layer["mixer"], layer["mlp"]["ff"]
+        nh, d, e = m["heads"], m["dim"], m["vdim"]
+        flops += 2 * tokens * 3 * F * W
+        if layer["type"] == "latent_attention":
+            r = m["kv_rank"]
+            # as computed here: queries carried into the latent space, attention over latents, results carried out
+            flops += 2 * tokens * ((nh * d + r + nh) * W + nh * d * r + nh * e * r + W * nh * e) + 4 * nh * r * pairs
+        else:
+            c = m["mask"]["size"]
+            full, rest = divmod(tokens, c)
+            seen = full * (c * (c + 1) // 2) + rest * (rest + 1) // 2
+            flops += 2 * tokens * ((nh * d + m["kv_heads"] * (d + e) + nh) * W + W * nh * e) + 2 * nh * (d + e) * seen
+    return flops
+
+
+def sulepel_kernel_rows(pk, llama):
+    """Each kernel the design adds, alone, beside the like kernel of the Llama path at the same sizes: microseconds
+    (median of 100 launches over rotating tensors) and the share of the measured copy bandwidth that the bytes it must
+    move make."""
+    import torch
+
+    from lyapunov_engine_b200 import ops
+
+    dev = "cuda:0"
+    W, nh, nkv, hd, F = llama["hidden_size"], llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"], llama["intermediate_size"]
+    r, page = SULEPEL_LATENT, BLOCK_SIZE
+    rows = []
+
+    def median_us(launch, sets):
+        for i in range(25):
+            launch(i % sets)
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(100)]
+        torch.cuda.synchronize()
+        for i, (a, b) in enumerate(events):
+            a.record()
+            launch(i % sets)
+            b.record()
+        torch.cuda.synchronize()
+        times = sorted(a.elapsed_time(b) * 1e3 for a, b in events)
+        return times[len(times) // 2]
+
+    def row(kernel, like, tokens, nbytes, launch, sets):
+        us = median_us(launch, sets)
+        rows.append({"kernel": kernel, "like": like, "tokens": tokens, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+                     "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)})
+
+    def sets_for(nbytes):
+        return max(2, min(64, (256 << 20) // max(nbytes, 1) + 1))
+
+    bf = torch.bfloat16
+    status = ops.new_status(dev)
+    for T in (8, 2048):
+        # norms
+        nbytes = T * W * (4 + 2 + 4 + 2) + 4 * W
+        n = sets_for(nbytes)
+        resid = [torch.randn(T, W, device=dev) for _ in range(n)]
+        delta = [torch.randn(T, W, device=dev).to(bf) for _ in range(n)]
+        out = [torch.empty(T, W, device=dev, dtype=bf) for _ in range(n)]
+        weight = torch.ones(W, device=dev)
+        row("rmsnorm in 4 groups + residual", "", T, nbytes, lambda i: ops.rmsnorm(out[i], resid[i], delta[i], weight, 1e-5, groups=4), n)
+        row("rmsnorm + residual", "rmsnorm in 4 groups + residual", T, nbytes, lambda i: ops.rmsnorm(out[i], resid[i], delta[i], weight, 1e-5), n)
+        # the short convolution (4 taps): reads and writes the rows once, the state of every request once
+        reqs = T if T <= 64 else 1
+        q_lens = [T // reqs] * reqs
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        treq = torch.tensor([b for b, m in enumerate(q_lens) for _ in range(0, m, 16)], dtype=torch.int32, device=dev)
+        tq0 = torch.tensor([s0 for m in q_lens for s0 in range(0, m, 16)], dtype=torch.int32, device=dev)
+        slots = torch.arange(reqs, dtype=torch.int32, device=dev)
+        state = torch.zeros(reqs + 1, 3, W, device=dev)
+        taps = torch.randn(4, W, device=dev)
+        nbytes = T * W * 4 + reqs * 3 * W * 8 + 16 * W
+        row("short convolution, 4 taps", "", T, nbytes, lambda i: ops.short_conv(delta[i], out[i], taps, state, slots, cu, treq, tq0, treq.numel()), n)
+        # embeddings
+        table = torch.randn(32000, W, device=dev).to(bf)
+        ids = torch.randint(0, 32000, (T,), dtype=torch.int32, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        rates = torch.rand((W + 1) // 2, device=dev)
+        nbytes = T * W * 6
+        row("embedding + sinusoid", "", T, nbytes, lambda i: ops.embed_sinusoid(resid[i], table, ids, pos, rates, status), n)
+        row("embedding", "embedding + sinusoid", T, nbytes, lambda i: ops.embed(resid[i], table, ids, status), n)
+        del resid, delta, out
+        # cache writes: the latent with its norm, unrotated keys and values, and the rotary write of the Llama path
+        pages = (T + page - 1) // page + 1
+        btab = torch.arange(pages, dtype=torch.int32, device=dev).view(1, -1).contiguous()
+        req0 = torch.zeros(T, dtype=torch.int32, device=dev)
+        width_l = nh * hd + r + 8
+        proj = torch.randn(T, width_l, device=dev).to(bf)
+        lat = torch.zeros(pages + 1, 1, page, r, device=dev, dtype=bf)
+        wn = torch.ones(r, device=dev)
+        row("latent norm + cache write", "", T, T * r * 4, lambda i: ops.latent_norm_store(proj, nh * hd, r, wn, 1e-5, lat, pos, req0, btab, page, status), 1)
+        qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=dev).to(bf)
+        kc = torch.zeros(pages + 1, nkv, page, hd, device=dev, dtype=bf)
+        vc = torch.zeros_like(kc)
+        row("key/value cache write", "", T, T * 2 * nkv * hd * 4, lambda i: ops.kv_store(qkv, nh * hd, (nh + nkv) * hd, kc, vc, pos, req0, btab, nkv, hd, page, status), 1)
+        cos_sin = torch.randn(max(T, 16), hd, device=dev)
+        row("rotary + key/value cache write", "latent norm + cache write; key/value cache write", T, T * ((nh + nkv) * hd * 4 + nkv * hd * 4),
+            lambda i: ops.rope_kv_write(qkv, kc, vc, cos_sin, pos, req0, btab, nh, nkv, hd, page, True, status), 1)
+        # per-head products and the gate
+        w_into = torch.randn(nh, r, hd, device=dev).to(bf)
+        w_out = torch.randn(nh, hd, r, device=dev).to(bf)
+        ql = torch.empty(T, nh * r, device=dev, dtype=bf)
+        ho = torch.empty(T, nh * hd, device=dev, dtype=bf)
+        gate = torch.randn(T, nh, device=dev).to(bf)
+        nbytes = 2 * (nh * r * hd + T * nh * (hd + r))
+        if T <= 64:
+            row("per-head product into the latent space (FP32 pipes)", "", T, nbytes, lambda i: ops.gemm_heads(ql, proj[:, :nh * hd], w_into), 1)
+            row("per-head product out of it, with gate (FP32 pipes)", "", T, nbytes, lambda i: ops.gemm_heads(ho, ql, w_out, gate), 1)
+        else:
+            row("per-head gate", "", T, T * nh * hd * 4, lambda i: ops.head_gate(ho, gate, nh, hd), 1)
+        # gated products
+        x = torch.randn(T, W, device=dev).to(bf)
+        wgu = [torch.randn(2 * F, W, device=dev).to(bf) for _ in range(4)]
+        act = torch.empty(T, F, device=dev, dtype=bf)
+        nbytes = 2 * (2 * F * W + T * W + T * F)
+        ws = None
+        from lyapunov_engine_b200.engine.runtime import Workspace
+        ws = Workspace(torch.device(dev))
+        row("gate/up product, clamped activation", "", T, nbytes, lambda i: ops.gated_linear(act, x, wgu[i], ws, status, (ops.GLU_CLAMPED, 1.702, 7.0)), 4)
+        row("gate/up product, SiLU", "gate/up product, clamped activation", T, nbytes, lambda i: ops.gated_linear(act, x, wgu[i], ws, status), 4)
+        del wgu
+    # decode attention, 8 requests at 4,096 keys: all heads over one pool of latents, beside grouped-query attention
+    B, ctx = 8, 4096
+    pages = B * ctx // page
+    btab = torch.arange(pages, dtype=torch.int32, device=dev).view(B, -1).contiguous()
+    cu = torch.arange(B + 1, dtype=torch.int32, device=dev)
+    before = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+    lat = torch.randn(pages + 1, 1, page, r, device=dev).to(bf)
+    q = torch.randn(B, nh * r, device=dev).to(bf)
+    o = torch.empty(B, nh * r, device=dev, dtype=bf)
+    from lyapunov_engine_b200.parts import attention_kernels as ak
+    splits = ak.decode_splits(B, nh, 1, ctx, r)
+    floats = ops.attention_decode_scratch_floats(r, B, nh, splits)
+    scratch = torch.zeros(max(floats, 1), device=dev)
+    row(f"decode attention over latents ({nh} heads on one pool of {r}, {splits} splits)", "", B, 2 * B * ctx * r,
+        lambda i: ops.attention_decode_bf16(o, scratch, q, q.stride(0), lat, lat, btab, cu, before, None, B, nh, 1, r, page, 0, hd ** -0.5, splits, status), 1)
+    kc = torch.randn(pages + 1, nkv, page, hd, device=dev).to(bf)
+    vc = torch.randn(pages + 1, nkv, page, hd, device=dev).to(bf)
+    q2 = torch.randn(B, nh * hd, device=dev).to(bf)
+    o2 = torch.empty(B, nh * hd, device=dev, dtype=bf)
+    splits2 = ak.decode_splits(B, nh, nkv, ctx, hd)
+    scratch2 = torch.zeros(max(ops.attention_decode_scratch_floats(hd, B, nh, splits2), 1), device=dev)
+    hs = torch.rand(nh, device=dev) + 0.5
+    row(f"decode attention, {nh} heads of {hd} in {nkv} groups ({splits2} splits)", "decode attention over latents", B, 2 * B * ctx * 2 * nkv * hd,
+        lambda i: ops.attention_decode_bf16(o2, scratch2, q2, q2.stride(0), kc, vc, btab, cu, before, None, B, nh, nkv, hd, page, 0, hd ** -0.5, splits2, status), 1)
+    row("the same with a factor per head and chunks", "", B, 2 * B * ((ctx - 1) % SULEPEL_CHUNK + 1) * 2 * nkv * hd,
+        lambda i: ops.attention_decode_bf16(o2, scratch2, q2, q2.stride(0), kc, vc, btab, cu, before, None, B, nh, nkv, hd, page, -SULEPEL_CHUNK, hd ** -0.5,
+                                            ak.decode_splits(B, nh, nkv, SULEPEL_CHUNK, hd), status, head_scale=hs), 1)
+    ops.check_status(status)
+    return rows
+
+
+def run_sulepel(args):
+    """--only sulepel: decode (1 and 8 requests at --context) and prefill (2,048 tokens) of a Sulepel model beside the
+    Llama model of the same width, feed-forward size, heads, layers and vocabulary (random weights, bfloat16), and
+    the design's own kernels alone beside their likes."""
+    global BLOCK_SIZE
+    import torch
+
+    BLOCK_SIZE = args.page
+    pk = peaks()
+    context = args.context or CONTEXT
+    out = {"only": "sulepel", "peaks": pk["source"], "context": context, "sizes": {}}
+    for name in ([args.shapes] if args.shapes != "1b" or args.layers else ["1b", "3b"]):
+        llama = dict(SHAPES[name])
+        if args.layers:
+            llama["num_hidden_layers"] = args.layers
+        su = sulepel_config(llama)
+        res = {}
+        for label, cfg in (("sulepel", su), ("llama", llama)):
+            rig = make_rig(cfg, context, 8, args.page)
+            for b in (1, 8):
+                rig.timed_decode(b, 3, 2, context - 200)
+                ms, graph_steps, _ = rig.timed_decode(b, 24, 6, context)
+                nbytes = sulepel_decode_bytes(cfg, b, context - 12) if label == "sulepel" else decode_bytes(cfg, b, context - 12)
+                res[f"{label}_decode_b{b}_ms"] = round(ms, 4)
+                res[f"{label}_decode_b{b}_tokens_per_s"] = round(b * 1000.0 / ms, 1)
+                res[f"{label}_decode_b{b}_hbm_frac"] = round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                res[f"{label}_decode_b{b}_graph_steps"] = graph_steps
+            ms = rig.timed_prefill(PREFILL_TOKENS, 3, 2)
+            flops = sulepel_prefill_flops(cfg, PREFILL_TOKENS) if label == "sulepel" else prefill_flops(cfg, PREFILL_TOKENS)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_ms"] = round(ms, 3)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_tokens_per_s"] = round(PREFILL_TOKENS * 1000.0 / ms, 1)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_bf16_frac"] = round(flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+            rig.close()
+            del rig
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+        for k, v in res.items():
+            print(f"{name}  {k} = {v}", file=sys.stderr)
+    rows = sulepel_kernel_rows(pk, dict(SHAPES["1b"]))
+    for r in rows:
+        print("  ".join(f"{k}={v}" for k, v in r.items() if v != ""), file=sys.stderr)
+    out["kernels"] = rows
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -769,11 +1008,12 @@ def main():
     p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels"], default=None,
+    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels", "sulepel"], default=None,
                    help="run one kind of step and exit (for profilers and for further sizes); mixed = --batch decoding "
                         "requests beside one --tokens portion of a prompt in every step; serving = the reference's "
                         "serving benchmark (small model, prompts of 128 tokens, 32 generated: TTFT, ITL, tokens/s); "
-                        "kernels = its kernel benchmark (RMSNorm and prefill attention over a grid of sizes)")
+                        "kernels = its kernel benchmark (RMSNorm and prefill attention over a grid of sizes); "
+                        "sulepel = the Sulepel design beside Llama at equal sizes (decode, prefill, its kernels alone)")
     p.add_argument("--batch-sizes", nargs="+", type=int, default=[1, 4, 8, 16], help="with --only serving")
     p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
@@ -798,6 +1038,8 @@ def main():
         return run_serving(args)
     if args.only == "kernels" and args.impl == "ours":
         return run_kernels(args)
+    if args.only == "sulepel" and args.impl == "ours":
+        return run_sulepel(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

@@ -19,7 +19,7 @@ from dataclasses import dataclass
 
 import torch
 
-from .. import build
+from .. import build, ops
 
 
 @dataclass
@@ -62,12 +62,20 @@ class DeviceCache:
             self.streams.append(pools)
         self.states = [torch.zeros((self.max_num_seqs + 1, *need.shape), dtype=need.dtype or torch.float32,
                                    device=runtime.device) for need in model.states]
+        self._state_table = ops.state_table(self.states)       # for zeroing fresh requests' rows in one launch
         self._bindings = []
         for run in model.runs:
             kv = self.streams[run.group][run.stream] if run.group is not None else None
             state = self.states[run.state] if run.state is not None else None
             extra = {name: self.states[index] for name, index in run.extra_states}
             self._bindings.append(CacheBinding(kv, run.writes, state, extra))
+
+    def zero_fresh_states(self, ctx) -> None:
+        """A request whose first tokens are in this step starts from zero
+        state in every buffer, whoever held its slot before."""
+        if self.states:
+            ops.zero_fresh_states(self._state_table, len(self.states), self.max_num_seqs + 1, ctx.state_slots,
+                                  ctx.ctx_before, ctx.num_requests)
 
     def binding(self, run_index: int) -> CacheBinding:
         return self._bindings[run_index]

@@ -175,9 +175,11 @@ __device__ __forceinline__ float gated_activation(float g, float u, const GatedA
   if (a.kind == 1) {
     g = fminf(g, a.limit);
     u = fminf(fmaxf(u, -a.limit), a.limit) + 1.0f;
-    return g / (1.0f + (FAST_EXP ? __expf(-a.slope * g) : expf(-a.slope * g))) * u;
+    if constexpr (FAST_EXP) return __fdividef(g, 1.0f + __expf(-a.slope * g)) * u;
+    return g / (1.0f + expf(-a.slope * g)) * u;
   }
-  return g / (1.0f + (FAST_EXP ? __expf(-g) : expf(-g))) * u;
+  if constexpr (FAST_EXP) return __fdividef(g, 1.0f + __expf(-g)) * u;
+  return g / (1.0f + expf(-g)) * u;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

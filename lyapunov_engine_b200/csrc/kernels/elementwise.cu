@@ -67,15 +67,27 @@ __global__ void glu_kernel(T *__restrict__ out, const T *__restrict__ gu, int64_
 
 // x[t, h, :] *= sigmoid(gate[t, h]): one number per token and head scales that
 // head's `head_width` values.  Sigmoid and product are 32-bit, rounded once.
-template <typename T>
+// VEC values per thread and access (16 bytes where VEC > 1; head_width, the
+// row strides and the base address then are multiples of VEC values).
+template <typename T, int VEC>
 __global__ void head_gate_kernel(T *__restrict__ x, int64_t x_stride, const T *__restrict__ gate, int64_t gate_stride,
-                                 int num_heads, int head_width) {
-  const int t = blockIdx.x;
-  const int row = num_heads * head_width;
-  for (int i = threadIdx.x; i < row; i += blockDim.x) {
-    const float g = le::to_f32(gate[t * gate_stride + i / head_width]);
-    T *p = x + t * x_stride + i;
-    *p = le::from_f32<T>(le::to_f32(*p) / (1.0f + expf(-g)));
+                                 int num_tokens, int num_heads, int head_width) {
+  const int per_row = num_heads * head_width / VEC;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<int64_t>(num_tokens) * per_row) return;
+  const int64_t t = idx / per_row;
+  const int i = static_cast<int>(idx - t * per_row) * VEC;
+  const float g = le::to_f32(gate[t * gate_stride + i / head_width]);
+  const float s = 1.0f / (1.0f + expf(-g));
+  T *p = x + t * x_stride + i;
+  if constexpr (VEC == 1) {
+    *p = le::from_f32<T>(le::to_f32(*p) * s);
+  } else {
+    uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) e[v] = le::from_f32<T>(le::to_f32(e[v]) * s);
+    *reinterpret_cast<uint4 *>(p) = raw;
   }
 }
 
@@ -130,6 +142,22 @@ __global__ void zero_fresh_state_kernel(uint32_t *__restrict__ state, int64_t ro
   for (int64_t i = threadIdx.x; i < row_words; i += blockDim.x) row[i] = 0u;
 }
 
+// The same for several state buffers in one launch (blockIdx.y: the buffer).  `table` holds, per buffer, its
+// address and the bytes of one of its rows.
+struct StateBuffer {
+  uint32_t *base;
+  int64_t row_words;
+};
+__global__ void zero_fresh_states_kernel(const StateBuffer *__restrict__ table, int num_rows,
+                                         const int32_t *__restrict__ slots, const int32_t *__restrict__ ctx_before) {
+  const int b = blockIdx.x;
+  const int slot = slots[b];
+  if (slot < 0 || slot >= num_rows || ctx_before[b] != 0) return;
+  const StateBuffer buffer = table[blockIdx.y];
+  uint32_t *row = buffer.base + static_cast<int64_t>(slot) * buffer.row_words;
+  for (int64_t i = threadIdx.x; i < buffer.row_words; i += blockDim.x) row[i] = 0u;
+}
+
 }  // namespace
 
 // How many multiprocessors the current device has (grids are sized by it).
@@ -147,6 +175,18 @@ LE_API int le_zero_fresh_state(void *state, int64_t row_bytes, int num_rows, con
   if (row_bytes % 4) return le::invalid("le_zero_fresh_state: rows of %lld bytes are not a multiple of 4", (long long)row_bytes);
   zero_fresh_state_kernel<<<num_requests, 256, 0, stream>>>(static_cast<uint32_t *>(state), row_bytes / 4, num_rows, slots,
                                                             ctx_before);
+  return le::launched();
+}
+
+// table: `num_buffers` pairs of 64-bit integers on the device (address of a buffer of [num_rows, row] bytes; the
+// row's size in 4-byte words).  One launch zeroes the fresh requests' rows of all of them.
+LE_API int le_zero_fresh_states(const void *table, int num_buffers, int num_rows, const int32_t *slots,
+                                const int32_t *ctx_before, int num_requests, cudaStream_t stream) {
+  if (num_requests <= 0 || num_buffers <= 0) return 0;
+  if (num_buffers > 65535) return le::invalid("le_zero_fresh_states: %d buffers are too many for one launch", num_buffers);
+  static_assert(sizeof(StateBuffer) == 16, "two 64-bit words per buffer");
+  zero_fresh_states_kernel<<<dim3(num_requests, num_buffers), 256, 0, stream>>>(static_cast<const StateBuffer *>(table), num_rows,
+                                                                                slots, ctx_before);
   return le::launched();
 }
 
@@ -188,10 +228,19 @@ LE_API int le_glu(void *out, const void *gate_up, int dtype, int num_tokens, int
 LE_API int le_head_gate(void *x, int64_t x_stride, const void *gate, int64_t gate_stride, int dtype, int num_tokens,
                         int num_heads, int head_width, cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  LE_DISPATCH_DTYPE(dtype, T,
-                    head_gate_kernel<T><<<num_tokens, 256, 0, stream>>>(static_cast<T *>(x), x_stride,
-                                                                        static_cast<const T *>(gate), gate_stride,
-                                                                        num_heads, head_width));
+  const int vec = dtype == LE_BF16 ? 8 : 4;
+  const bool wide = head_width % vec == 0 && x_stride % vec == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  const int64_t items = static_cast<int64_t>(num_tokens) * num_heads * head_width / (wide ? vec : 1);
+  const int64_t blocks = (items + 255) / 256;
+  if (blocks > 2147483647LL) return le::invalid("le_head_gate: too many elements for one launch");
+#define LE_GO(T, V)                                                                                                  \
+  head_gate_kernel<T, V><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(static_cast<T *>(x), x_stride,           \
+                                                                            static_cast<const T *>(gate), gate_stride, \
+                                                                            num_tokens, num_heads, head_width)
+  if (dtype == LE_BF16) { if (wide) LE_GO(__nv_bfloat16, 8); else LE_GO(__nv_bfloat16, 1); }
+  else if (dtype == LE_F32) { if (wide) LE_GO(float, 4); else LE_GO(float, 1); }
+  else return le::invalid("le_head_gate: unknown dtype code %d", dtype);
+#undef LE_GO
   return le::launched();
 }
 

@@ -11,9 +11,14 @@
 // attended latent out of it (w = the head's value map), where the per-head
 // output gate rides in the epilogue.
 //
-// Every output is one chain of fused multiply-adds over ascending k in 32
-// bits, whatever the number of rows, so a token's result does not depend on
-// its batch.  Inputs float32 or bfloat16; the result is rounded once.
+// Two forms.  Many rows: tiles of 32 rows x 64 columns through shared memory,
+// every output one chain of fused multiply-adds over ascending k.  Few rows (a
+// decode step): no shared memory and no block-wide barrier; a warp takes four
+// output columns of a head, its lanes share out k (each reads 16-byte pieces of
+// the weight rows, which lie contiguous in k), and the lanes' partial sums meet
+// in a shuffle tree.  In both forms a row's result is the same whatever rows
+// stand beside it.  Sums are 32-bit; inputs float32 or bfloat16; the result is
+// rounded once.
 #include "common.cuh"
 
 namespace {
@@ -70,12 +75,88 @@ gemm_heads_kernel(T *__restrict__ out, int64_t out_stride, const T *__restrict__
   }
 }
 
+constexpr int GR_ROWS = 8;      // rows of a a block takes (blockIdx.z walks the rest)
+constexpr int GR_COLS = 4;      // output columns per warp
+constexpr int GR_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(GR_WARPS * 32)
+gemm_heads_rows_kernel(T *__restrict__ out, int64_t out_stride, const T *__restrict__ a, int64_t a_stride,
+                       const T *__restrict__ w, const T *__restrict__ gate, int64_t gate_stride, int M, int N, int K) {
+  constexpr int VEC = 16 / sizeof(T);
+  le::let_successor_start();
+  const int head = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (blockIdx.x * GR_WARPS + warp) * GR_COLS;
+  const int m0 = blockIdx.z * GR_ROWS;
+  const int rows = min(GR_ROWS, M - m0);
+  if (n0 >= N) return;
+  const T *wh = w + (static_cast<int64_t>(head) * N + n0) * K;
+  float acc[GR_ROWS][GR_COLS] = {};
+  le::wait_for_predecessor();
+  // lanes take pieces of VEC consecutive k; K is a multiple of VEC (checked by the launcher)
+  for (int k = lane * VEC; k < K; k += 32 * VEC) {
+    float wv[GR_COLS][VEC];
+#pragma unroll
+    for (int c = 0; c < GR_COLS; ++c) {
+      if (n0 + c < N) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(wh + static_cast<int64_t>(c) * K + k);
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) wv[c][v] = le::to_f32(e[v]);
+      } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) wv[c][v] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < GR_ROWS; ++r) {
+      if (r < rows) {
+        const uint4 raw = *reinterpret_cast<const uint4 *>(a + (m0 + r) * a_stride + static_cast<int64_t>(head) * K + k);
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          const float x = le::to_f32(e[v]);
+#pragma unroll
+          for (int c = 0; c < GR_COLS; ++c) acc[r][c] = fmaf(x, wv[c][v], acc[r][c]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < GR_ROWS; ++r)
+#pragma unroll
+    for (int c = 0; c < GR_COLS; ++c) acc[r][c] = le::warp_sum(acc[r][c]);
+  if (lane < GR_COLS && n0 + lane < N) {
+    for (int r = 0; r < rows; ++r) {
+      float g = 1.0f;
+      if (gate) g = 1.0f / (1.0f + expf(-le::to_f32(gate[(m0 + r) * gate_stride + head])));
+      float v = acc[r][0];
+#pragma unroll
+      for (int c = 1; c < GR_COLS; ++c) v = lane == c ? acc[r][c] : v;
+      out[(m0 + r) * out_stride + static_cast<int64_t>(head) * N + n0 + lane] = le::from_f32<T>(v * g);
+    }
+  }
+}
+
 }  // namespace
+
+// Up to this many rows the form without shared memory runs (where the operands' rows can be read in 16-byte pieces).
+constexpr int GEMM_HEADS_FEW_ROWS = 32;
 
 LE_API int le_gemm_heads(void *out, int64_t out_stride, const void *a, int64_t a_stride, const void *w, const void *gate,
                          int64_t gate_stride, int dtype, int M, int heads, int N, int K, cudaStream_t stream) {
   if (M <= 0 || heads <= 0 || N <= 0) return 0;
   if (K <= 0) return le::invalid("le_gemm_heads: K must be positive");
+  const int vec = dtype == LE_BF16 ? 8 : 4;
+  if (M <= GEMM_HEADS_FEW_ROWS && K % vec == 0 && a_stride % vec == 0 && heads <= 65535 &&
+      ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0) {
+    const dim3 few((N + GR_WARPS * GR_COLS - 1) / (GR_WARPS * GR_COLS), heads, (M + GR_ROWS - 1) / GR_ROWS);
+    LE_DISPATCH_DTYPE(dtype, T,
+                      return le::launch_chained(gemm_heads_rows_kernel<T>, few, dim3(GR_WARPS * 32), 0, stream,
+                                                static_cast<T *>(out), out_stride, static_cast<const T *>(a), a_stride,
+                                                static_cast<const T *>(w), static_cast<const T *>(gate), gate_stride, M, N, K));
+  }
   const dim3 grid((M + GH_BM - 1) / GH_BM, (N + GH_BN - 1) / GH_BN, heads);
   if (grid.y > 65535 || grid.z > 65535) return le::invalid("le_gemm_heads: too many columns or heads for one launch");
   LE_DISPATCH_DTYPE(dtype, T,

@@ -130,9 +130,8 @@ class Model:
     def forward(self, ctx, cache):
         """Logits [wanted rows, vocab] float32 (None when nothing is wanted).
         ``cache.binding(run_index)`` gives each run its pages and state."""
-        for state in cache.states:
-            # a request whose first tokens are in this step starts from zero state, whoever held its slot before
-            ops.zero_fresh_state(state, ctx.state_slots, ctx.ctx_before, ctx.num_requests)
+        # a request whose first tokens are in this step starts from zero state, whoever held its slot before
+        cache.zero_fresh_states(ctx)
         resid = self.embedding.forward(ctx)
         stream = ResidualStream(resid)
         for index, run in enumerate(self.runs):

@@ -66,6 +66,7 @@ _attention: dict[int, ctypes.CDLL] = {}
 _CORE_SIGNATURES = {
     "le_embed": [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_zero_fresh_state": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "le_zero_fresh_states": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
     "le_sm_count": [],
     "le_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
@@ -206,6 +207,27 @@ def zero_fresh_state(state: torch.Tensor, state_slots: torch.Tensor, ctx_before:
                                       num_requests, _stream()), "le_zero_fresh_state")
 
 
+def state_table(states: list) -> torch.Tensor | None:
+    """What zero_fresh_states() takes: per state buffer its address and the
+    4-byte words of one of its rows, as int64 pairs on the device."""
+    if not states:
+        return None
+    rows = states[0].shape[0]
+    flat = []
+    for s in states:
+        _need_cuda(s)
+        assert s.is_contiguous() and s.shape[0] == rows and (s[0].numel() * s.element_size()) % 4 == 0
+        flat += [s.data_ptr(), s[0].numel() * s.element_size() // 4]
+    return torch.tensor(flat, dtype=torch.int64, device=states[0].device)
+
+
+def zero_fresh_states(table: torch.Tensor, num_buffers: int, num_rows: int, state_slots: torch.Tensor,
+                      ctx_before: torch.Tensor, num_requests: int) -> None:
+    """zero_fresh_state() for all of a model's state buffers in one launch."""
+    _check(core().le_zero_fresh_states(_ptr(table), num_buffers, num_rows, _ptr(state_slots), _ptr(ctx_before),
+                                       num_requests, _stream()), "le_zero_fresh_states")
+
+
 _sm_count: dict[int, int] = {}
 
 
@@ -275,7 +297,9 @@ def short_conv(out, h, w_taps, state, state_slots, cu_q, tile_request, tile_q0, 
     each request from its state row.  ``w_taps``: float32 [taps, channels];
     ``state``: float32 [rows, taps - 1, channels] (None when taps is 1), row
     ``state_slots[b]`` holds request b's last taps - 1 inputs and is brought up
-    to date; the tiles list SHORT_CONV_TILE tokens each."""
+    to date; the tiles list SHORT_CONV_TILE tokens each.  ``tile_request`` and
+    ``tile_q0`` None: every request of the step brings one token (request b is
+    row b), ``num_tiles`` is their number."""
     _need_cuda(out, h, w_taps, state, state_slots, cu_q)
     T, C = h.shape
     taps = w_taps.shape[0]

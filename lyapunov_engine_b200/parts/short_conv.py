@@ -43,6 +43,10 @@ class CausalTaps(InputFilter):
 
     def forward(self, x, ctx, state):
         out = ctx.workspace.get("filtered", tuple(x.shape), x.dtype)
-        tile_request, tile_q0, num_tiles, _ = ctx.tiles[ops.SHORT_CONV_TILE]
-        ops.short_conv(out, x, self.weight, state, ctx.state_slots, ctx.cu_q, tile_request, tile_q0, num_tiles)
+        if ctx.pure_decode:
+            # one token per request: request b is row b, no tile list to read
+            ops.short_conv(out, x, self.weight, state, ctx.state_slots, ctx.cu_q, None, None, ctx.num_requests)
+        else:
+            tile_request, tile_q0, num_tiles, _ = ctx.tiles[ops.SHORT_CONV_TILE]
+            ops.short_conv(out, x, self.weight, state, ctx.state_slots, ctx.cu_q, tile_request, tile_q0, num_tiles)
         return out

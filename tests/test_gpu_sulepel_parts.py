@@ -79,7 +79,7 @@ def test_short_convolution_under_every_cut(taps, dtype):
     w = (0.5 * torch.randn(C, taps, generator=g))
     seqs = [torch.randn(n, C, generator=g).to(dtype) for n in (37, 5, 64)]
     want = [ps.causal_taps(s.double(), w.double()).float() for s in seqs]
-    cuts = [[1, 1, 2, 17, 1, 3, 12], [2, 1, 1, 1], [33, 1, 1, 16, 2, 11]]
+    cuts = [[1, 1, 2, 1, 17, 1, 2, 12], [2, 1, 1, 1], [33, 1, 1, 1, 16, 1, 11]]
     slots_of = [2, 0, 3]
     state = torch.full((5, max(taps - 1, 1), C), 9.0, device=DEV) if taps > 1 else None    # stale inputs of earlier requests
     wt = w.t().contiguous().to(DEV)
@@ -97,7 +97,10 @@ def test_short_convolution_under_every_cut(taps, dtype):
             ops.zero_fresh_state(state, slots, before, len(live))       # what the framework does before a step
         out = torch.zeros_like(h)
         tr, tq, n = _tiles(q_lens, ops.SHORT_CONV_TILE)
-        ops.short_conv(out, h, wt, state, slots, cu, tr, tq, n)
+        if all(x == 1 for x in q_lens) and step % 2:
+            ops.short_conv(out, h, wt, state, slots, cu, None, None, len(q_lens))     # the form for steps of single tokens
+        else:
+            ops.short_conv(out, h, wt, state, slots, cu, tr, tq, n)
         o = 0
         for r, n in zip(live, q_lens):
             got[r].append(out[o:o + n].float().cpu())
@@ -159,7 +162,8 @@ def test_clamped_gated_activation_in_every_kernel(rows):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,heads,N,K", [(1, 3, 48, 24), (19, 5, 7, 130), (100, 2, 96, 40), (33, 1, 64, 64)])
+@pytest.mark.parametrize("rows,heads,N,K", [(1, 3, 48, 24), (19, 5, 7, 130), (100, 2, 96, 40), (33, 1, 64, 64), (8, 6, 50, 64),
+                                            (32, 2, 128, 16)])
 def test_per_head_products(rows, heads, N, K, dtype):
     from lyapunov_engine_b200 import ops
     g = torch.Generator().manual_seed(rows + K)
@@ -181,10 +185,11 @@ def test_per_head_products(rows, heads, N, K, dtype):
     ops.head_gate(plain, gate.to(DEV)[:, 1:1 + heads], heads, N)
     torch.testing.assert_close(plain.float().cpu(), gated.reshape(rows, -1).float(), **tol)
     if dtype == torch.float32:
-        # a row's result does not depend on the rows beside it
-        one = torch.zeros(1, heads * N, dtype=dtype, device=DEV)
-        ops.gemm_heads(one, a_dev[rows - 1:], w.to(DEV), gate.to(DEV)[rows - 1:, 1:1 + heads])
-        assert torch.equal(one[0], out[rows - 1])
+        # a row's result does not depend on the rows beside it (the kernel has a form for up to 32 rows and one for more)
+        few = 1 if rows <= 32 else 33
+        part = torch.zeros(few, heads * N, dtype=dtype, device=DEV)
+        ops.gemm_heads(part, a_dev[rows - few:], w.to(DEV), gate.to(DEV)[rows - few:, 1:1 + heads])
+        assert torch.equal(part[-1], out[rows - 1])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
