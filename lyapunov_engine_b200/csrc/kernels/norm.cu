@@ -17,6 +17,14 @@
 // `out`, and the residual stream is left as it is (the final norm before the
 // output head runs on the wanted rows alone).
 //
+// With taps (decode steps, one token per request, row b = request b): the
+// normed row then passes through a short causal convolution over time before it
+// is stored, out = h + sum_j w[j] * h(j steps back), whose earlier inputs are the
+// request's state row [taps - 1, channels] (oldest first), shifted here by the
+// new input.  Same arithmetic, order and roundings as the norm followed by the
+// convolution's own kernel (the normed value is rounded to the output type
+// before it enters the convolution and the state, as that path stores it).
+//
 // Reference: rmsnorm_kernel, csrc/kernels/fused_rmsnorm_swiglu.cu:15-113 (same
 // arithmetic; its residual stream has the activations' type, ours is 32-bit).
 #include "common.cuh"
@@ -54,14 +62,55 @@ __device__ __forceinline__ void store_vec(T *p, const float (&src)[VEC]) {
   }
 }
 
+struct TapsArgs {
+  const float *w = nullptr;        // [taps, channels]
+  float *state = nullptr;          // [num_state_rows, taps - 1, channels]
+  const int32_t *slots = nullptr;  // state row of each request (< 0: none; zeros before it, nothing kept)
+  int taps = 0, channels = 0, num_state_rows = 0;
+};
+
+// h: VEC normed values of channels channel .. channel + VEC of request `request`; replaced by the convolution's output.
+template <typename TO, int VEC>
+__device__ __forceinline__ void taps_step(float (&h)[VEC], const TapsArgs &t, int64_t channel, int request) {
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) h[v] = le::to_f32(le::from_f32<TO>(h[v]));
+  const int keep = t.taps - 1;
+  const int slot = t.slots[request];
+  float *mine = (slot >= 0 && slot < t.num_state_rows && keep > 0) ? t.state + (static_cast<int64_t>(slot) * keep) * t.channels + channel : nullptr;
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = h[v];
+  for (int s = 0; s < keep; ++s) {
+    float prev[VEC], wt[VEC];
+    load_vec<float, VEC>(wt, t.w + static_cast<int64_t>(s) * t.channels + channel);
+    if (mine) {
+      load_vec<float, VEC>(prev, mine + static_cast<int64_t>(s) * t.channels);
+      if (s > 0) store_vec<float, VEC>(mine + static_cast<int64_t>(s - 1) * t.channels, prev);
+    } else {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) prev[v] = 0.0f;
+    }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] = fmaf(wt[v], prev[v], acc[v]);
+  }
+  float wt[VEC];
+  load_vec<float, VEC>(wt, t.w + static_cast<int64_t>(keep) * t.channels + channel);
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = fmaf(wt[v], h[v], acc[v]);
+  if (mine) store_vec<float, VEC>(mine + static_cast<int64_t>(keep - 1) * t.channels, h);
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) h[v] = acc[v];
+}
+
 // PER_THREAD > 0: the row fits in PER_THREAD vectors of VEC values per thread, which stay in registers
 // between the sum of squares and the scaling (one pass over memory).  0: any width, two passes.
 // PARTIALS > 0: `num_partials` is this number, known when compiling, so that every load of a thread is asked
 // for before the first is used (a decode step's norm is one round trip to memory, not one per partial sum).
-template <typename TO, typename TD, int VEC, int PER_THREAD, int PARTIALS>
+// TAPS: the short convolution follows in the same kernel (PER_THREAD > 0 only).
+template <typename TO, typename TD, int VEC, int PER_THREAD, int PARTIALS, bool TAPS>
 __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, const TD *__restrict__ delta,
                                int num_partials, int64_t partial_stride, const float *__restrict__ weight,
-                               const int32_t *__restrict__ rows, float eps, int hidden, int row_width) {
+                               const int32_t *__restrict__ rows, float eps, int hidden, int row_width, TapsArgs taps) {
   // `hidden`: the values that share one root mean square (the row, or one of its equal parts: blockIdx.y);
   // `row_width`: the values of a whole row
   __shared__ float scratch[33];
@@ -113,6 +162,7 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
       if (i < hidden) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) w[it][v] = val[it][v] * inv * w[it][v];
+        if constexpr (TAPS) taps_step<TO, VEC>(w[it], taps, part + i, static_cast<int>(src_row));
         store_vec<TO, VEC>(o + i, w[it]);
       }
     }
@@ -148,6 +198,7 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
         load_vec<float, VEC>(w, weight + i);
 #pragma unroll
         for (int v = 0; v < VEC; ++v) w[v] = val[it][v] * inv * w[v];
+        if constexpr (TAPS) taps_step<TO, VEC>(w, taps, part + i, static_cast<int>(src_row));
         store_vec<TO, VEC>(o + i, w);
       }
     }
@@ -180,14 +231,22 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
 
 template <typename TO, typename TD>
 int launch(void *out, float *resid, const void *delta, int num_partials, int64_t partial_stride, const float *weight,
-           const int32_t *rows, float eps, int num_rows, int row_width, int groups, cudaStream_t stream) {
+           const int32_t *rows, float eps, int num_rows, int row_width, int groups, const TapsArgs &taps, cudaStream_t stream) {
   const int hidden = row_width / groups;
   int threads = 32;
   while (threads < 512 && threads * 8 < hidden) threads *= 2;
-#define LE_NORM_P(VEC, PER, PARTIALS)                                                                                  \
-  return le::launch_chained(rmsnorm_kernel<TO, TD, VEC, PER, PARTIALS>, dim3(num_rows, groups), dim3(threads), 0, stream, \
+#define LE_NORM_T(VEC, PER, PARTIALS, TAPS)                                                                             \
+  return le::launch_chained(rmsnorm_kernel<TO, TD, VEC, PER, PARTIALS, TAPS>, dim3(num_rows, groups), dim3(threads), 0, stream, \
                             static_cast<TO *>(out), resid, static_cast<const TD *>(delta), num_partials, partial_stride, \
-                            weight, rows, eps, hidden, row_width)
+                            weight, rows, eps, hidden, row_width, taps)
+#define LE_NORM_P(VEC, PER, PARTIALS)                                                                                  \
+  do {                                                                                                                 \
+    if constexpr (VEC == 4 && PER == 2) {                                                                              \
+      if (taps.w != nullptr) LE_NORM_T(VEC, PER, PARTIALS, true);                                                      \
+    }                                                                                                                  \
+    if (taps.w != nullptr) return le::invalid("le_rmsnorm_taps: rows of this width have no form with taps");           \
+    LE_NORM_T(VEC, PER, PARTIALS, false);                                                                              \
+  } while (0)
 #define LE_NORM(VEC, PER)                                                                                               \
   do {                                                                                                                  \
     if (PER > 0 && PER <= 2) {                                                                                          \
@@ -209,6 +268,7 @@ int launch(void *out, float *resid, const void *delta, int num_partials, int64_t
   LE_NORM(1, 0);
 #undef LE_NORM
 #undef LE_NORM_P
+#undef LE_NORM_T
 }
 
 }  // namespace
@@ -225,10 +285,43 @@ LE_API int le_rmsnorm(void *out, int out_dtype, float *resid, const void *delta,
   if (groups < 1 || groups > 65535 || hidden % groups)
     return le::invalid("le_rmsnorm: a row of %d values does not divide into %d equal parts", hidden, groups);
   if (delta != nullptr && num_partials < 1) return le::invalid("le_rmsnorm: num_partials must be at least 1");
-#define LE_GO(TO, TD) return launch<TO, TD>(out, resid, delta, num_partials, partial_stride, weight, rows, eps, num_rows, hidden, groups, stream)
+  const TapsArgs taps{};
+#define LE_GO(TO, TD) return launch<TO, TD>(out, resid, delta, num_partials, partial_stride, weight, rows, eps, num_rows, hidden, groups, taps, stream)
   if (out_dtype == LE_F32 && (delta == nullptr || delta_dtype == LE_F32)) LE_GO(float, float);
   if (out_dtype == LE_BF16 && (delta == nullptr || delta_dtype == LE_BF16)) LE_GO(__nv_bfloat16, __nv_bfloat16);
   if (out_dtype == LE_BF16 && delta_dtype == LE_F32) LE_GO(__nv_bfloat16, float);
 #undef LE_GO
   return le::invalid("le_rmsnorm: unsupported types: out %d, delta %d", out_dtype, delta_dtype);
+}
+
+// 1 when le_rmsnorm_taps has a form for rows of `hidden` values in `groups` parts.
+LE_API int le_rmsnorm_taps_applies(int hidden, int groups) {
+  if (groups < 1 || hidden % groups) return 0;
+  const int part = hidden / groups;
+  int threads = 32;
+  while (threads < 512 && threads * 8 < part) threads *= 2;
+  return part % 4 == 0 && (part / 4 + threads - 1) / threads <= 2 ? 1 : 0;
+}
+
+// le_rmsnorm over every row of a step whose requests bring one token each (row b is request b), followed in the same
+// kernel by a short causal convolution over time with per-request state: taps_w [taps, hidden] float32, state
+// [num_state_rows, taps - 1, hidden] float32, state_slots[b] the state row of request b (< 0: none).  All buffers
+// 16-byte aligned.
+LE_API int le_rmsnorm_taps(void *out, int out_dtype, float *resid, const void *delta, int delta_dtype, int num_partials,
+                           int64_t partial_stride, const float *weight, float eps, int num_rows, int hidden, int groups,
+                           const float *taps_w, float *state, int num_state_rows, const int32_t *state_slots, int num_taps,
+                           cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (!le_rmsnorm_taps_applies(hidden, groups)) return le::invalid("le_rmsnorm_taps: rows of %d values in %d parts have no form with taps", hidden, groups);
+  if (delta != nullptr && num_partials < 1) return le::invalid("le_rmsnorm_taps: num_partials must be at least 1");
+  if (num_taps < 1 || taps_w == nullptr || (num_taps > 1 && state == nullptr)) return le::invalid("le_rmsnorm_taps: %d taps need weights and state", num_taps);
+  if ((reinterpret_cast<uintptr_t>(taps_w) | reinterpret_cast<uintptr_t>(state)) & 15) return le::invalid("le_rmsnorm_taps: weights and state must be 16-byte aligned");
+  TapsArgs taps;
+  taps.w = taps_w, taps.state = state, taps.slots = state_slots, taps.taps = num_taps, taps.channels = hidden, taps.num_state_rows = num_state_rows;
+#define LE_GO(TO, TD) return launch<TO, TD>(out, resid, delta, num_partials, partial_stride, weight, nullptr, eps, num_rows, hidden, groups, taps, stream)
+  if (out_dtype == LE_F32 && (delta == nullptr || delta_dtype == LE_F32)) LE_GO(float, float);
+  if (out_dtype == LE_BF16 && (delta == nullptr || delta_dtype == LE_BF16)) LE_GO(__nv_bfloat16, __nv_bfloat16);
+  if (out_dtype == LE_BF16 && delta_dtype == LE_F32) LE_GO(__nv_bfloat16, float);
+#undef LE_GO
+  return le::invalid("le_rmsnorm_taps: unsupported types: out %d, delta %d", out_dtype, delta_dtype);
 }

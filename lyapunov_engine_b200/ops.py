@@ -72,6 +72,9 @@ _CORE_SIGNATURES = {
     "le_convert": [c_void_p, c_int, c_void_p, c_int, c_int64, c_void_p],
     "le_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_float, c_int,
                    c_int, c_int, c_void_p],
+    "le_rmsnorm_taps_applies": [c_int, c_int],
+    "le_rmsnorm_taps": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_float, c_int, c_int, c_int,
+                        c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p],
     "le_embed_sinusoid": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p],
     "le_head_gate": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p],
@@ -81,6 +84,8 @@ _CORE_SIGNATURES = {
                     c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_latent_norm_store": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+    "le_latent_prepare": [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p,
+                          c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_gemm_heads": [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
                       c_void_p],
     "le_gemm_tc_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
@@ -342,6 +347,37 @@ def latent_norm_store(src, col, rank, weight, eps, cache, positions, request_of_
                                        _ptr(status), _stream()), "le_latent_norm_store")
 
 
+LATENT_PREPARE_ROWS = 32
+
+
+def latent_prepare_applies(src: torch.Tensor, head_dim: int) -> bool:
+    """Whether latent_prepare() takes these rows (few of them, 16-byte pieces)."""
+    vec = 16 // src.element_size()
+    return (src.shape[0] <= LATENT_PREPARE_ROWS and head_dim % vec == 0 and src.stride(0) % vec == 0
+            and src.data_ptr() % 16 == 0 and src.stride(1) == 1)
+
+
+def latent_prepare(q_latent, src, w_into, col, rank, weight, eps, cache, positions, request_of_token, block_table,
+                   page_size, status) -> None:
+    """For a step of few rows, in one launch: gemm_heads(q_latent, src[:, :heads
+    * head_dim], w_into) and latent_norm_store(src, col, rank, ...) (``cache``
+    None: the latent is not stored)."""
+    _need_cuda(q_latent, src, w_into, weight, cache, positions, block_table)
+    heads, padded, head_dim = w_into.shape
+    T = src.shape[0]
+    assert latent_prepare_applies(src, head_dim) and w_into.is_contiguous() and w_into.dtype == src.dtype == q_latent.dtype
+    assert q_latent.shape == (T, heads * padded) and q_latent.stride(1) == 1 and padded >= rank
+    assert weight.dtype == torch.float32 and weight.numel() == rank and block_table.is_contiguous()
+    pages = 0
+    if cache is not None:
+        assert cache.dtype == src.dtype and cache.is_contiguous() and tuple(cache.shape[1:]) == (1, page_size, padded)
+        pages = cache.shape[0]
+    _check(core().le_latent_prepare(_ptr(src), src.stride(0), T, heads, head_dim, _ptr(w_into), _ptr(q_latent),
+                                    q_latent.stride(0), col, rank, padded, _ptr(weight), float(eps), _ptr(cache),
+                                    dtype_code(src.dtype), _ptr(positions), _ptr(request_of_token), _ptr(block_table),
+                                    block_table.shape[1], page_size, pages, _ptr(status), _stream()), "le_latent_prepare")
+
+
 def gemm_heads(out, a, w, gate=None) -> None:
     """One product per head: out[t, h, :] = w[h] @ a[t, h, :] (w: [heads, N,
     K]), times sigmoid(gate[t, h]) where ``gate`` is given.  ``a``, ``out`` and
@@ -394,6 +430,41 @@ def rmsnorm(out: torch.Tensor, resid: torch.Tensor, delta, weight: torch.Tensor,
         assert n == resid.shape[0]
     _check(core().le_rmsnorm(_ptr(out), dtype_code(out.dtype), _ptr(resid), _ptr(delta), dcode, parts, stride,
                              _ptr(weight), _ptr(rows), float(eps), n, H, int(groups), _stream()), "le_rmsnorm")
+
+
+def rmsnorm_taps_applies(hidden: int, groups: int) -> bool:
+    """Whether rmsnorm_taps() has a form for rows of this width and grouping."""
+    return bool(core().le_rmsnorm_taps_applies(int(hidden), int(groups)))
+
+
+def rmsnorm_taps(out, resid, delta, weight, eps, groups, w_taps, state, state_slots) -> None:
+    """rmsnorm() over every row of a step whose requests bring one token each
+    (row b is request b), then, in the same kernel, short_conv() of the normed
+    rows: same arithmetic and roundings as the two kernels one after the other."""
+    _need_cuda(out, resid, delta, weight, w_taps, state, state_slots)
+    n, H = out.shape
+    taps = w_taps.shape[0]
+    assert resid.dtype == torch.float32 and weight.dtype == torch.float32 and weight.numel() == H
+    assert out.is_contiguous() and resid.is_contiguous() and resid.shape == (n, H)
+    assert w_taps.dtype == torch.float32 and w_taps.is_contiguous() and w_taps.shape[1] == H
+    parts, stride, dcode = 1, 0, dtype_code(out.dtype)
+    if delta is not None:
+        assert delta.is_contiguous() and tuple(delta.shape[-2:]) == tuple(resid.shape)
+        if delta.dim() == 3:
+            assert delta.dtype == torch.float32
+            parts, stride = delta.shape[0], delta.stride(0)
+        else:
+            assert delta.dtype in (out.dtype, torch.float32)
+        dcode = dtype_code(delta.dtype)
+    rows = 0
+    if taps > 1:
+        assert state is not None and state.dtype == torch.float32 and state.is_contiguous()
+        assert tuple(state.shape[1:]) == (taps - 1, H)
+        rows = state.shape[0]
+    _check(core().le_rmsnorm_taps(_ptr(out), dtype_code(out.dtype), _ptr(resid), _ptr(delta), dcode, parts, stride,
+                                  _ptr(weight), float(eps), n, H, int(groups), _ptr(w_taps),
+                                  _ptr(state) if taps > 1 else None, rows, _ptr(state_slots), taps, _stream()),
+           "le_rmsnorm_taps")
 
 
 def rope_kv_write(qkv, k_cache, v_cache, cos_sin, positions, request_of_token, block_table, num_heads, num_kv_heads,

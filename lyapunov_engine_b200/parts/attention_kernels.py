@@ -21,7 +21,7 @@ from .. import ops
 MAX_HEAD_DIM = 512              # of the FP32-pipe kernel; the tensor-core kernels end at 128
 GENERIC_TILE = 16
 PREFILL_TILE = 128
-DECODE_KEYS_PER_SPLIT = 256     # a split is worth its launch from about four tiles of keys
+DECODE_KEYS_PER_SPLIT = int(os.environ.get("LYAPUNOV_DECODE_KEYS_PER_SPLIT", "256"))     # a split is worth its launch from about four tiles of keys
 DECODE_MAX_SPLITS = 64
 USE_TC_ATTENTION = os.environ.get("LYAPUNOV_TC_ATTENTION", "1") not in ("0", "")
 # 0: a partly filled step of fixed shape cuts the keys as the full step does (one graph per shape)
@@ -118,7 +118,8 @@ def keys_bound(context_bound: int, reach: int) -> int:
     return min(context_bound, abs(reach)) if reach else context_bound
 
 
-def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int, reach: int = 0):
+def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, context_bound: int, reach: int = 0,
+                   max_splits: int = DECODE_MAX_SPLITS):
     """The split count (and the kernel's form, where it is not the usual one)
     of a step in which ``fill`` of the one-token requests are real: dummy
     requests finish at once, so the real ones alone fill the waves (9 real
@@ -126,13 +127,13 @@ def decode_variant(fill: int, num_heads: int, num_kv_heads: int, head_dim: int, 
     if not SPLITS_BY_FILL or not ops.attention_mma_available(head_dim):
         return None
     fill = max(1, fill)
-    splits = decode_splits(fill, num_heads, num_kv_heads, keys_bound(context_bound, reach), head_dim)
+    splits = min(max_splits, decode_splits(fill, num_heads, num_kv_heads, keys_bound(context_bound, reach), head_dim))
     # (the kernel's form follows the real requests too)
     return (splits, "small") if decode_small_form(fill, num_heads, num_kv_heads, head_dim) else splits
 
 
 def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, reach, scale, head_scale=None,
-        head_scale_positive: bool = True) -> None:
+        head_scale_positive: bool = True, max_splits: int = DECODE_MAX_SPLITS) -> None:
     """``reach``: which keys a query sees (ops.reach_code); ``head_scale``: one
     more factor per query head on its scores (float32 [num_heads]) or None.
     The tcgen05 kernel folds that factor into its exponent's scale and so takes
@@ -149,8 +150,8 @@ def run(out, qkv, ctx, kv, num_heads, num_kv_heads, head_dim, reach, scale, head
                     num_kv_heads, head_dim, kv.page_size, window, scale, ctx.status, head_scale=head_scale)
         if ctx.num_decode:
             real = min(ctx.decode_fill, ctx.num_decode) if SPLITS_BY_FILL else 0     # dummy requests finish at once
-            splits = decode_splits(real or ctx.num_decode, num_heads, num_kv_heads, keys_bound(ctx.context_bound, reach),
-                                   head_dim)
+            splits = min(max_splits, decode_splits(real or ctx.num_decode, num_heads, num_kv_heads,
+                                                   keys_bound(ctx.context_bound, reach), head_dim))
             small = decode_small_form(real or ctx.num_decode, num_heads, num_kv_heads, head_dim)
             floats = ops.attention_decode_scratch_floats(head_dim, ctx.num_decode, num_heads, splits)
             scratch = ctx.workspace.get("attention_scratch", (floats,), torch.float32) if floats else None

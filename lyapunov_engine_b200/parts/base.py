@@ -37,6 +37,8 @@ Interfaces (all tensors are CUDA tensors; T tokens in the step, H width):
     ``forward(x, ctx, state) -> x'``: what a block puts between a norm and the
     sub-layer that reads it (a short convolution over time, say); it may keep
     per-request state of its own (``state_need()``), which the block hands it.
+    Optional: ``after_norm(norm, resid, delta, ctx, state) -> x' | None`` runs
+    the norm before it and itself as one kernel where it can (None: it cannot).
 ``FeedForward``
     ``forward(x, ctx) -> y``.
 ``Block``

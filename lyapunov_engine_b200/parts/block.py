@@ -47,9 +47,18 @@ class PreNormBlock(Block):
             p.bind(get, runtime)
 
     def forward(self, stream, ctx, cache) -> None:
-        n = self.mixer_norm.apply(stream.resid, stream.pending, workspace=ctx.workspace)
+        n = None
         if self.mixer_input is not None:
-            n = self.mixer_input.forward(n, ctx, (cache.extra or {}).get("mixer_input"))
+            # an input filter may know how to run the norm before it in its own kernel
+            state = (cache.extra or {}).get("mixer_input")
+            fused = getattr(self.mixer_input, "after_norm", None)
+            if fused is not None:
+                n = fused(self.mixer_norm, stream.resid, stream.pending, ctx, state)
+            if n is None:
+                n = self.mixer_input.forward(self.mixer_norm.apply(stream.resid, stream.pending, workspace=ctx.workspace),
+                                             ctx, state)
+        else:
+            n = self.mixer_norm.apply(stream.resid, stream.pending, workspace=ctx.workspace)
         a = self.mixer.forward(n, ctx, cache)
         if self.feed_forward is None:
             stream.pending = a

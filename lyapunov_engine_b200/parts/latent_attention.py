@@ -25,6 +25,8 @@ as the other many-row products do.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
@@ -33,6 +35,10 @@ from .attention import signed_scale
 from .base import KVNeed, Mixer, TensorDecl, register_mixer
 
 LIBRARY_ROWS = 64       # bfloat16 steps with more rows than this run the per-head products in the library
+# The most ways a decoded token's latents are cut.  (Capping it at 8, the most that merge inside a thread-block
+# cluster without a second kernel, was measured and is slower: all heads of a request share one pool, so a request is
+# two blocks before splitting, and 512 keys a block cost more than the merge kernel: 1.03 against 0.93 ms a step.)
+MAX_DECODE_SPLITS = int(os.environ.get("LYAPUNOV_LATENT_SPLITS", str(attention_kernels.DECODE_MAX_SPLITS)))
 
 
 @register_mixer("latent_attention")
@@ -62,7 +68,8 @@ class LatentAttentionMixer(Mixer):
     def decode_variant(self, fill, num_decode, context_bound):
         if self.runtime is None or self.runtime.dtype != torch.bfloat16:
             return None
-        return attention_kernels.decode_variant(fill, self.num_heads, 1, self.padded_latent, context_bound, self.reach)
+        return attention_kernels.decode_variant(fill, self.num_heads, 1, self.padded_latent, context_bound, self.reach,
+                                                MAX_DECODE_SPLITS)
 
     def tensors(self):
         q, down, norm, uk, uv, o = self.names
@@ -124,14 +131,20 @@ class LatentAttentionMixer(Mixer):
         proj = ws.get("latent_proj", (T, self.w_in.shape[0]), rt.dtype)
         ops.linear(proj, x, self.w_in, ctx.status)
         kv = cache.kv
-        if cache.write:
-            ops.latent_norm_store(proj, self.latent_col, r, self.norm_weight, self.norm_eps, kv.k, ctx.positions,
-                                  ctx.request_of_token, ctx.block_tables[kv.group], kv.page_size, ctx.status)
         q_latent = ws.get("latent_q", (T, nh * rp), rt.dtype)
-        self._per_head(q_latent, proj[:, :self.q_width], self.w_into, None, nh)
+        if ops.latent_prepare_applies(proj, self.qk_dim):
+            # few rows: the latent's norm and store and the queries' way into the latent space as one launch
+            ops.latent_prepare(q_latent, proj, self.w_into, self.latent_col, r, self.norm_weight, self.norm_eps,
+                               kv.k if cache.write else None, ctx.positions, ctx.request_of_token,
+                               ctx.block_tables[kv.group], kv.page_size, ctx.status)
+        else:
+            if cache.write:
+                ops.latent_norm_store(proj, self.latent_col, r, self.norm_weight, self.norm_eps, kv.k, ctx.positions,
+                                      ctx.request_of_token, ctx.block_tables[kv.group], kv.page_size, ctx.status)
+            self._per_head(q_latent, proj[:, :self.q_width], self.w_into, None, nh)
         attended = ws.get("latent_attn", (T, nh * rp), rt.dtype)
         attention_kernels.run(attended, q_latent, ctx, kv, nh, 1, rp, self.reach, self.kernel_scale, self.head_scale,
-                              self.head_scale_positive)
+                              self.head_scale_positive, max_splits=MAX_DECODE_SPLITS)
         heads_out = ws.get("attn", (T, nh * e), rt.dtype)
         gate = proj[:, self.gate_col:self.gate_col + nh] if self.gate_name else None
         self._per_head(heads_out, attended, self.w_out_of, gate, nh)

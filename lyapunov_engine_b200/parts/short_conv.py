@@ -11,10 +11,16 @@ cut into steps.  The weight is stored [channels, taps] and kept transposed,
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import ops
 from .base import InputFilter, StateNeed, TensorDecl, register_input_filter
+
+
+# 0: the norm before the filter and the filter always run as two kernels
+FUSE_WITH_NORM = os.environ.get("LYAPUNOV_FUSE_TAPS", "1") not in ("0", "")
 
 
 @register_input_filter("causal_taps")
@@ -40,6 +46,21 @@ class CausalTaps(InputFilter):
     def bind(self, get, runtime):
         self.weight = get(self.weight_name).t().contiguous()        # [taps, channels]
         self.runtime = runtime
+
+    def after_norm(self, norm, resid, delta, ctx, state):
+        """The norm before this filter and the filter as one kernel, where that
+        exists: steps whose requests all bring one token, an RMS norm (whole
+        or in groups) over rows the kernel holds in registers.  None: nothing
+        was done, the caller runs the norm and forward()."""
+        if not (FUSE_WITH_NORM and ctx.pure_decode and ctx.num_tokens == ctx.num_requests):
+            return None
+        if getattr(norm, "weight", None) is None or not hasattr(norm, "groups") or norm.hidden_size != self.channels:
+            return None
+        if not ops.rmsnorm_taps_applies(self.channels, norm.groups):
+            return None
+        out = ctx.workspace.get("filtered", (ctx.num_tokens, self.channels), self.runtime.dtype)
+        ops.rmsnorm_taps(out, resid, delta, norm.weight, norm.eps, norm.groups, self.weight, state, ctx.state_slots)
+        return out
 
     def forward(self, x, ctx, state):
         out = ctx.workspace.get("filtered", tuple(x.shape), x.dtype)

@@ -122,6 +122,44 @@ def test_short_convolution_under_every_cut(taps, dtype):
         assert torch.equal(kept, state)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,groups,taps,partials", [(96, 3, 4, 0), (2048, 4, 4, 2), (320, 1, 2, 1), (4096, 2, 3, 4), (128, 4, 1, 3)])
+def test_norm_and_convolution_as_one_kernel(width, groups, taps, partials, dtype):
+    """Decode steps run the norm and the short convolution as one kernel: the
+    same bits as the two kernels, outputs and state, over several steps, with
+    a row that stands for no request."""
+    from lyapunov_engine_b200 import ops
+    assert ops.rmsnorm_taps_applies(width, groups)
+    g = torch.Generator().manual_seed(width + taps)
+    B = 5
+    w = (1.0 + 0.3 * torch.randn(width, generator=g)).to(DEV)
+    wt = (0.5 * torch.randn(taps, width, generator=g)).to(DEV)
+    slots = torch.tensor([3, 0, -1, 5, 1], dtype=torch.int32, device=DEV)
+    cu = torch.arange(B + 1, dtype=torch.int32, device=DEV)
+    states = [torch.randn(7, max(taps - 1, 1), width, generator=g).to(DEV) if taps > 1 else None for _ in range(2)]
+    if taps > 1:
+        states[1].copy_(states[0])
+    for step in range(4):
+        x = torch.randn(B, width, generator=g)
+        if partials == 0:
+            delta = None
+        elif partials == 1:
+            delta = torch.randn(B, width, generator=g).to(dtype).to(DEV)
+        else:
+            delta = torch.randn(partials, B, width, generator=g).to(DEV)
+        resid = [x.clone().to(DEV), x.clone().to(DEV)]
+        normed = torch.zeros(B, width, dtype=dtype, device=DEV)
+        two = torch.zeros(B, width, dtype=dtype, device=DEV)
+        ops.rmsnorm(normed, resid[0], delta, w, 1e-5, groups=groups)
+        ops.short_conv(two, normed, wt, states[0], slots, cu, None, None, B)
+        one = torch.zeros(B, width, dtype=dtype, device=DEV)
+        ops.rmsnorm_taps(one, resid[1], delta, w, 1e-5, groups, wt, states[1], slots)
+        assert torch.equal(one, two) and torch.equal(resid[0], resid[1])
+        if taps > 1:
+            assert torch.equal(states[0], states[1])
+    assert not ops.rmsnorm_taps_applies(66, 2)       # parts that are no multiple of four values: the two kernels run
+
+
 @pytest.mark.parametrize("rows", [1, 7, 16, 29, 64, 200, 700])
 def test_clamped_gated_activation_in_every_kernel(rows):
     """The stand-alone kernel (both types), and in bfloat16 the product kernels
@@ -231,6 +269,42 @@ def test_cache_writes(dtype):
     ops.kv_store(src.to(DEV), 8, 8 + nkv * hd, k, v, positions.to(DEV), request.to(DEV), bad.to(DEV), nkv, hd, page, status)
     with pytest.raises(ops.KernelError):
         ops.check_status(status)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,heads,d,rank", [(1, 3, 24, 48), (8, 8, 32, 128), (19, 2, 16, 20), (32, 5, 64, 72)])
+def test_latent_prepare_equals_its_two_kernels(rows, heads, d, rank, dtype):
+    from lyapunov_engine_b200 import ops
+    g = torch.Generator().manual_seed(rows + rank)
+    padded = (rank + 15) // 16 * 16
+    col = (heads * d + 7) // 8 * 8
+    src = torch.randn(rows, col + (rank + 7) // 8 * 8 + 8, generator=g).to(dtype).to(DEV)
+    w_into = torch.zeros(heads, padded, d)
+    w_into[:, :rank] = torch.randn(heads, rank, d, generator=g) / math.sqrt(d)
+    w_into = w_into.to(dtype).to(DEV)
+    weight = (1.0 + 0.3 * torch.randn(rank, generator=g)).to(DEV)
+    page, pages = 4, 12
+    positions = torch.arange(5, 5 + rows, dtype=torch.int32, device=DEV)
+    request = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    table = torch.randperm(pages - 1, generator=g)[:10].to(torch.int32).view(1, 10).to(DEV)
+    status = ops.new_status(DEV)
+    caches = [torch.full((pages, 1, page, padded), 3.0, dtype=dtype, device=DEV) for _ in range(2)]
+    two = torch.zeros(rows, heads * padded, dtype=dtype, device=DEV)
+    ops.latent_norm_store(src, col, rank, weight, 1e-5, caches[0], positions, request, table, page, status)
+    ops.gemm_heads(two, src[:, :heads * d], w_into)
+    one = torch.zeros_like(two)
+    assert ops.latent_prepare_applies(src, d)
+    ops.latent_prepare(one, src, w_into, col, rank, weight, 1e-5, caches[1], positions, request, table, page, status)
+    ops.check_status(status)
+    assert torch.equal(one, two) and torch.equal(caches[0], caches[1])
+    want = torch.einsum("thk,hnk->thn", src[:, :heads * d].double().cpu().view(rows, heads, d), w_into.double().cpu())
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(one.float().cpu(), want.reshape(rows, -1).float(), **tol)
+    # a run that reads another run's cache stores nothing
+    kept = caches[1].clone()
+    caches[1].fill_(1.0)
+    ops.latent_prepare(one, src, w_into, col, rank, weight, 1e-5, None, positions, request, table, page, status)
+    assert float((caches[1].float() - 1.0).abs().max()) == 0.0 and torch.equal(one, two) and kept is not None
 
 
 # ---------------------------------------------------------------- attention over chunks, a factor per head
