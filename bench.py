@@ -821,8 +821,8 @@ def sulepel_prefill_flops(cfg, tokens):
 
 def sulepel_kernel_rows(pk, llama):
     """Each kernel the design adds, alone, beside the like kernel of the Llama path at the same sizes: microseconds
-    (median of 100 launches over rotating tensors) and the share of the measured copy bandwidth that the bytes it must
-    move make."""
+    per launch inside a captured graph, over rotating tensors, and the share of the measured copy bandwidth that the
+    bytes it must move make."""
     import torch
 
     from lyapunov_engine_b200 import ops
@@ -833,16 +833,26 @@ def sulepel_kernel_rows(pk, llama):
     rows = []
 
     def median_us(launch, sets):
-        for i in range(25):
+        """Microseconds per launch inside a captured graph of at least 16 launches over rotating tensors (a launch
+        by itself from the host costs more than these kernels run; inside a step they are nodes of such a graph)."""
+        n = max(sets, 16)
+        for i in range(n):
             launch(i % sets)
-        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(100)]
         torch.cuda.synchronize()
-        for i, (a, b) in enumerate(events):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(n):
+                launch(i % sets)
+        for _ in range(3):
+            graph.replay()
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(15)]
+        torch.cuda.synchronize()
+        for a, b in events:
             a.record()
-            launch(i % sets)
+            graph.replay()
             b.record()
         torch.cuda.synchronize()
-        times = sorted(a.elapsed_time(b) * 1e3 for a, b in events)
+        times = sorted(a.elapsed_time(b) * 1e3 / n for a, b in events)
         return times[len(times) // 2]
 
     def row(kernel, like, tokens, nbytes, launch, sets):
@@ -965,6 +975,18 @@ def run_sulepel(args):
     BLOCK_SIZE = args.page
     pk = peaks()
     context = args.context or CONTEXT
+    if args.profile_step:
+        # a few steps launch by launch (no captured graph) of a model of --layers layers (4 by default), for a profiler
+        llama = dict(SHAPES[args.shapes])
+        llama["num_hidden_layers"] = args.layers or 4
+        rig = make_rig(sulepel_config(llama), context, 8, args.page)
+        rig.runner.use_cuda_graphs = False
+        if args.profile_step == "decode":
+            ms, _, _ = rig.timed_decode(args.batch, 2, 2, context)
+        else:
+            ms = rig.timed_prefill(args.tokens or PREFILL_TOKENS, 1, 2)
+        print(json.dumps({"only": "sulepel", "profile_step": args.profile_step, "layers": llama["num_hidden_layers"], "ms": round(ms, 3)}))
+        return 0
     out = {"only": "sulepel", "peaks": pk["source"], "context": context, "sizes": {}}
     for name in ([args.shapes] if args.shapes != "1b" or args.layers else ["1b", "3b"]):
         llama = dict(SHAPES[name])
@@ -1026,6 +1048,9 @@ def main():
     p.add_argument("--no-cuda-graphs", action="store_true", help="with --only decode: launch every kernel by itself")
     p.add_argument("--without", choices=["norms", "qkv", "attention", "o", "gate_up", "down", "head"], default=None,
                    help="with --only decode (batches up to 16): time the step with this kind of kernel left out")
+    p.add_argument("--profile-step", choices=["decode", "prefill"], default=None,
+                   help="with --only sulepel: run a few steps of that kind launch by launch (no captured graph) on a model of "
+                        "--layers layers (4 by default) and exit; for profilers")
     p.add_argument("--points", choices=["all", "1b"], default="all",
                    help="all: also decode, prefill and the mixed step at the 3B and 8B shapes (context 8192) in `points`")
     args = p.parse_args()

@@ -46,10 +46,13 @@ __global__ void embed_sinusoid_kernel(float *__restrict__ out, const T *__restri
   const bool bad = id < 0 || id >= vocab;
   if (bad && threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_TOKEN);
   const T *src = table + static_cast<int64_t>(bad ? 0 : id) * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float angle = p * rates[i >> 1];
-    const float wave = (i & 1) ? cosf(angle) : sinf(angle);
-    dst[i] = bad ? 0.0f : le::to_f32(src[i]) + wave;
+  // a thread takes the two entries that share an angle: one sincosf for both
+  for (int pair = threadIdx.x; 2 * pair < hidden; pair += blockDim.x) {
+    float s, c;
+    sincosf(p * rates[pair], &s, &c);
+    const int i = 2 * pair;
+    dst[i] = bad ? 0.0f : le::to_f32(src[i]) + s;
+    if (i + 1 < hidden) dst[i + 1] = bad ? 0.0f : le::to_f32(src[i + 1]) + c;
   }
 }
 

@@ -24,13 +24,12 @@ __device__ __forceinline__ void gemm_heads_rows_block(T *__restrict__ out, int64
   if (n0 >= N) return;
   const T *wh = w + (static_cast<int64_t>(head) * N + n0) * K;
   float acc[GR_ROWS][GR_COLS] = {};
-  le::wait_for_predecessor();
-  // lanes take pieces of VEC consecutive k; K is a multiple of VEC (checked by the launcher)
-  for (int k = lane * VEC; k < K; k += 32 * VEC) {
-    float wv[GR_COLS][VEC];
+  // lanes take pieces of VEC consecutive k; K is a multiple of VEC (checked by the launcher).  The weights do not
+  // depend on the kernel before this one: a lane's first pieces of them are asked for before the wait for it.
+  auto load_weights = [&](float (&wv)[GR_COLS][VEC], int k) {
 #pragma unroll
     for (int c = 0; c < GR_COLS; ++c) {
-      if (n0 + c < N) {
+      if (n0 + c < N && k < K) {
         const uint4 raw = *reinterpret_cast<const uint4 *>(wh + static_cast<int64_t>(c) * K + k);
         const T *e = reinterpret_cast<const T *>(&raw);
 #pragma unroll
@@ -40,6 +39,12 @@ __device__ __forceinline__ void gemm_heads_rows_block(T *__restrict__ out, int64
         for (int v = 0; v < VEC; ++v) wv[c][v] = 0.0f;
       }
     }
+  };
+  float wv[GR_COLS][VEC];
+  load_weights(wv, lane * VEC);
+  le::wait_for_predecessor();
+  for (int k = lane * VEC; k < K; k += 32 * VEC) {
+    if (k != lane * VEC) load_weights(wv, k);
 #pragma unroll
     for (int r = 0; r < GR_ROWS; ++r) {
       if (r < rows) {

@@ -102,6 +102,61 @@ __device__ __forceinline__ void taps_step(float (&h)[VEC], const TapsArgs &t, in
   for (int v = 0; v < VEC; ++v) h[v] = acc[v];
 }
 
+// The same in two halves for up to TAPS_AHEAD taps: what does not depend on the normed values (weights, old state)
+// is asked for before the row's sum of squares is known, so that those loads run beside the reduction.
+constexpr int TAPS_AHEAD = 4;
+template <int VEC>
+struct TapsFetched {
+  float w[TAPS_AHEAD][VEC];
+  float prev[TAPS_AHEAD - 1][VEC];
+  float *mine;
+};
+template <int VEC>
+__device__ __forceinline__ void taps_fetch(TapsFetched<VEC> &f, const TapsArgs &t, int64_t channel, int request) {
+  const int keep = t.taps - 1;
+  const int slot = t.slots[request];
+  f.mine = (slot >= 0 && slot < t.num_state_rows && keep > 0) ? t.state + (static_cast<int64_t>(slot) * keep) * t.channels + channel : nullptr;
+#pragma unroll
+  for (int s = 0; s < TAPS_AHEAD; ++s)
+    if (s < t.taps) load_vec<float, VEC>(f.w[s], t.w + static_cast<int64_t>(s) * t.channels + channel);
+#pragma unroll
+  for (int s = 0; s < TAPS_AHEAD - 1; ++s) {
+    if (s < keep && f.mine) {
+      load_vec<float, VEC>(f.prev[s], f.mine + static_cast<int64_t>(s) * t.channels);
+    } else {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) f.prev[s][v] = 0.0f;
+    }
+  }
+}
+template <typename TO, int VEC>
+__device__ __forceinline__ void taps_apply(float (&h)[VEC], const TapsFetched<VEC> &f, const TapsArgs &t) {
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) h[v] = le::to_f32(le::from_f32<TO>(h[v]));
+  const int keep = t.taps - 1;
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = h[v];
+#pragma unroll
+  for (int s = 0; s < TAPS_AHEAD - 1; ++s) {
+    if (s < keep) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[v] = fmaf(f.w[s][v], f.prev[s][v], acc[v]);
+      if (f.mine && s > 0) store_vec<float, VEC>(f.mine + static_cast<int64_t>(s - 1) * t.channels, f.prev[s]);
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < TAPS_AHEAD; ++s) {
+    if (s == keep) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) acc[v] = fmaf(f.w[s][v], h[v], acc[v]);
+    }
+  }
+  if (f.mine) store_vec<float, VEC>(f.mine + static_cast<int64_t>(keep - 1) * t.channels, h);
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) h[v] = acc[v];
+}
+
 // PER_THREAD > 0: the row fits in PER_THREAD vectors of VEC values per thread, which stay in registers
 // between the sum of squares and the scaling (one pass over memory).  0: any width, two passes.
 // PARTIALS > 0: `num_partials` is this number, known when compiling, so that every load of a thread is asked
@@ -138,6 +193,17 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
         load_vec<float, VEC>(w[it], weight + i);
       }
     }
+    TapsFetched<VEC> ahead[TAPS ? PER_THREAD : 1];
+    const bool fetch_ahead = TAPS && taps.taps <= TAPS_AHEAD;
+    if constexpr (TAPS) {
+      if (fetch_ahead) {
+#pragma unroll
+        for (int it = 0; it < PER_THREAD; ++it) {
+          const int i = (it * blockDim.x + threadIdx.x) * VEC;
+          if (i < hidden) taps_fetch<VEC>(ahead[it], taps, part + i, static_cast<int>(src_row));
+        }
+      }
+    }
     float ss = 0.0f;
 #pragma unroll
     for (int it = 0; it < PER_THREAD; ++it) {
@@ -162,7 +228,10 @@ __global__ void rmsnorm_kernel(TO *__restrict__ out, float *__restrict__ resid, 
       if (i < hidden) {
 #pragma unroll
         for (int v = 0; v < VEC; ++v) w[it][v] = val[it][v] * inv * w[it][v];
-        if constexpr (TAPS) taps_step<TO, VEC>(w[it], taps, part + i, static_cast<int>(src_row));
+        if constexpr (TAPS) {
+          if (fetch_ahead) taps_apply<TO, VEC>(w[it], ahead[it], taps);
+          else taps_step<TO, VEC>(w[it], taps, part + i, static_cast<int>(src_row));
+        }
         store_vec<TO, VEC>(o + i, w[it]);
       }
     }
