@@ -55,9 +55,14 @@ CONFIGS = {
            "layers": [latent(4, 32, 32, 64, 0.18, dense(256, 2.0)),
                       chunked(4, 2, 64, 64, 100, 0.125, dense(256, 2.0)),
                       latent(2, 64, 32, 128, 0.12, dense(128, 1.2))]}, 16),
+    # sizes no kernel takes in 16-byte pieces (heads of 20 and 12), a latent beyond the tensor-core kernels' head sizes
+    # (136 -> 144: the FP32-pipe attention also in bfloat16), five taps, a width of 72 in three parts
+    "d": ({"architecture": "Sulepel", "vocab": 130, "width": 72, "norm": {"eps": 1e-5, "groups": 3}, "canon": {"taps": 5},
+           "layers": [latent(2, 20, 12, 136, 0.22, dense(56, 1.8)),
+                      chunked(2, 1, 12, 20, 25, 0.3, dense(40, 2.2))]}, 8),
 }
-LENGTHS = {"a": (23, 47, 75, 141), "b": (9, 70, 35, 101), "c": (40, 130, 301, 215)}
-PROMPTS = {"a": (3, 30, 41, 100), "b": (1, 64, 2, 67), "c": (8, 128, 260, 101)}
+LENGTHS = {"a": (23, 47, 75, 141), "b": (9, 70, 35, 101), "c": (40, 130, 301, 215), "d": (12, 66, 31, 90)}
+PROMPTS = {"a": (3, 30, 41, 100), "b": (1, 64, 2, 67), "c": (8, 128, 260, 101), "d": (2, 40, 30, 51)}
 
 
 def write_folder(folder, cfg, weights, dtype):

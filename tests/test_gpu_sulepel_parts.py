@@ -68,14 +68,13 @@ def _tiles(q_lens, size):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("taps", [1, 2, 3, 4, 7])
-def test_short_convolution_under_every_cut(taps, dtype):
+@pytest.mark.parametrize("taps,C", [(1, 200), (2, 200), (3, 200), (4, 200), (7, 200), (3, 52), (17, 36)])
+def test_short_convolution_under_every_cut(taps, C, dtype):
     """Three requests are fed in cuts of unequal sizes (down to one token, and
     shorter than the taps), in batches, with state slots that another request
     left its inputs in; the result equals the convolution of each whole sequence."""
     from lyapunov_engine_b200 import ops
-    C = 200
-    g = torch.Generator().manual_seed(taps)
+    g = torch.Generator().manual_seed(taps)       # (52 and 36 channels: no 16-byte pieces, one channel a thread)
     w = (0.5 * torch.randn(C, taps, generator=g))
     seqs = [torch.randn(n, C, generator=g).to(dtype) for n in (37, 5, 64)]
     want = [ps.causal_taps(s.double(), w.double()).float() for s in seqs]
@@ -123,7 +122,8 @@ def test_short_convolution_under_every_cut(taps, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,groups,taps,partials", [(96, 3, 4, 0), (2048, 4, 4, 2), (320, 1, 2, 1), (4096, 2, 3, 4), (128, 4, 1, 3)])
+@pytest.mark.parametrize("width,groups,taps,partials", [(96, 3, 4, 0), (2048, 4, 4, 2), (320, 1, 2, 1), (4096, 2, 3, 4), (128, 4, 1, 3),
+                                                        (256, 2, 6, 2), (64, 1, 5, 5)])
 def test_norm_and_convolution_as_one_kernel(width, groups, taps, partials, dtype):
     """Decode steps run the norm and the short convolution as one kernel: the
     same bits as the two kernels, outputs and state, over several steps, with
