@@ -37,7 +37,7 @@ def test_sinusoid_embedding():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,groups", [(96, 1), (96, 3), (320, 5), (66, 2), (4096, 4)])
+@pytest.mark.parametrize("width,groups", [(96, 1), (96, 3), (360, 5), (66, 2), (4096, 4)])
 def test_norm_in_groups(width, groups, dtype):
     from lyapunov_engine_b200 import ops
     g = torch.Generator().manual_seed(width + groups)
@@ -122,7 +122,7 @@ def test_short_convolution_under_every_cut(taps, C, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width,groups,taps,partials", [(96, 3, 4, 0), (2048, 4, 4, 2), (320, 1, 2, 1), (4096, 2, 3, 4), (128, 4, 1, 3),
+@pytest.mark.parametrize("width,groups,taps,partials", [(96, 3, 4, 0), (2048, 4, 4, 2), (352, 1, 2, 1), (4096, 2, 3, 4), (128, 4, 1, 3),
                                                         (256, 2, 6, 2), (64, 1, 5, 5)])
 def test_norm_and_convolution_as_one_kernel(width, groups, taps, partials, dtype):
     """Decode steps run the norm and the short convolution as one kernel: the
