@@ -51,7 +51,7 @@ class SulepelConfig:
     width: int
     norm_eps: float
     norm_groups: int
-    taps: int
+    taps: int                      # 0: no input convolution
     layers: tuple[SulepelLayer, ...]
     raw: dict
 
@@ -60,7 +60,9 @@ class SulepelConfig:
         r = KeyReader(raw, source)
         width = r.integer("width")
         norm = KeyReader(r.mapping("norm"), source + ": norm")
-        canon = KeyReader(r.mapping("canon"), source + ": canon")
+        # (a config without "canon" describes a model without the input convolution)
+        raw_canon = r.mapping("canon", None)
+        canon = KeyReader(raw_canon if raw_canon is not None else {"taps": 0}, source + ": canon")
         groups = norm.integer("groups")
         if width % groups:
             raise ConfigError(f"{source}: width {width} does not divide into norm.groups {groups}")
@@ -79,10 +81,11 @@ class SulepelConfig:
                 mixer = SulepelMixer(kind, m.integer("heads"), m.integer("dim"), m.integer("vdim"),
                                      m.number("scale", positive=False), kv_rank=m.integer("kv_rank"))
             elif kind == "attention":
-                mask = KeyReader(m.mapping("mask"), where + ".mixer.mask")
+                # (a mixer without "mask" sees every earlier key)
+                mask = m.mapping("mask", None)
+                chunk = KeyReader(mask, where + ".mixer.mask").integer("size") if mask is not None else 0
                 mixer = SulepelMixer(kind, m.integer("heads"), m.integer("dim"), m.integer("vdim"),
-                                     m.number("scale", positive=False), kv_heads=m.integer("kv_heads"),
-                                     chunk=mask.integer("size"))
+                                     m.number("scale", positive=False), kv_heads=m.integer("kv_heads"), chunk=chunk)
                 if mixer.heads % mixer.kv_heads:
                     raise ConfigError(f"{where}.mixer: {mixer.heads} heads do not divide into {mixer.kv_heads} kv_heads")
             else:
@@ -96,5 +99,5 @@ class SulepelConfig:
                 ff = SulepelFeedForward(ff_kind, f.integer("ff"), f.number("limit"))
             layers.append(SulepelLayer(mixer, ff))
         return SulepelConfig(architecture=r.string("architecture"), vocab=r.integer("vocab"), width=width,
-                             norm_eps=norm.number("eps"), norm_groups=groups, taps=canon.integer("taps"),
+                             norm_eps=norm.number("eps"), norm_groups=groups, taps=canon.integer("taps", minimum=0),
                              layers=tuple(layers), raw=dict(raw))

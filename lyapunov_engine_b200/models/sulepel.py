@@ -42,7 +42,7 @@ def sulepel_spec(raw_config: dict) -> ModelSpec:
         else:
             mixer = PartSpec("attention", {
                 "hidden_size": W, "num_heads": m.heads, "num_kv_heads": m.kv_heads, "head_dim": m.dim,
-                "value_dim": m.vdim, "position": None, "scale": m.scale, "chunk": m.chunk,
+                "value_dim": m.vdim, "position": None, "scale": m.scale, "chunk": m.chunk or None,
                 "q_name": p + "mix.q", "k_name": p + "mix.k", "v_name": p + "mix.v", "o_name": p + "mix.o",
                 "head_scale_name": p + "mix.temp", "gate_name": p + "mix.g"})
         feed_forward = feed_forward_norm = None
@@ -55,7 +55,8 @@ def sulepel_spec(raw_config: dict) -> ModelSpec:
         layers.append(LayerSpec(PartSpec("prenorm", {
             "mixer": mixer, "feed_forward": feed_forward, "mixer_norm": norm(p + "norm1"),
             "feed_forward_norm": feed_forward_norm,
-            "mixer_input": PartSpec("causal_taps", {"channels": W, "taps": c.taps, "weight_name": p + "canon1"})})))
+            "mixer_input": (PartSpec("causal_taps", {"channels": W, "taps": c.taps, "weight_name": p + "canon1"})
+                            if c.taps else None)})))
     return ModelSpec(
         architecture=c.architecture,
         hidden_size=W,

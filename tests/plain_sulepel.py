@@ -110,7 +110,8 @@ def chunked_attention(h, w, p, cfg, round_to=None) -> torch.Tensor:
     k = k.repeat_interleave(rep, dim=0)
     v = v.repeat_interleave(rep, dim=0)
     scale = float(cfg["scale"]) * w[p + "temp"].to(h.dtype)
-    o = masked_softmax_attention(q, k, v, scale, chunk_mask(T, int(cfg["mask"]["size"])))
+    visible = chunk_mask(T, int(cfg["mask"]["size"])) if cfg.get("mask") else causal_mask(T)
+    o = masked_softmax_attention(q, k, v, scale, visible)
     gate = torch.sigmoid(_r(h @ w[p + "g"].T, round_to))
     o = _r(o.transpose(0, 1) * gate[:, :, None], round_to).reshape(T, H * e)
     return _r(o @ w[p + "o"].T, round_to)
@@ -139,7 +140,8 @@ def forward(cfg: dict, w: dict, ids, dtype=torch.float64, round_to=None, layers_
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}."
         h = _r(grouped_rmsnorm(x, w[p + "norm1"], eps, groups), round_to)
-        h = _r(causal_taps(h, w[p + "canon1"]), round_to)
+        if cfg.get("canon"):
+            h = _r(causal_taps(h, w[p + "canon1"]), round_to)
         if layer["type"] == "latent_attention":
             x = x + latent_attention(h, w, p + "mix.", layer["mixer"], eps, round_to)
         elif layer["type"] == "attention":
@@ -171,12 +173,13 @@ def greedy(cfg: dict, w: dict, prompt, steps: int, dtype=torch.float64) -> list[
 # --------------------------------------------------------------------------
 def tensor_shapes(cfg: dict) -> dict[str, tuple]:
     W, V = int(cfg["width"]), int(cfg["vocab"])
-    taps = int(cfg["canon"]["taps"])
+    taps = int(cfg["canon"]["taps"]) if cfg.get("canon") else 0
     shapes = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
         shapes[p + "norm1"] = (W,)
-        shapes[p + "canon1"] = (W, taps)
+        if taps:
+            shapes[p + "canon1"] = (W, taps)
         H, d, e = m["heads"], m["dim"], m["vdim"]
         if layer["type"] == "latent_attention":
             r = m["kv_rank"]

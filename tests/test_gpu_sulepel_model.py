@@ -65,9 +65,14 @@ CONFIGS = {
     "e": ({"architecture": "Sulepel", "vocab": 77, "width": 100, "norm": {"eps": 1e-5, "groups": 5}, "canon": {"taps": 3},
            "layers": [chunked(2, 2, 8, 8, 5, 0.35, dense(36, 2.0)),
                       latent(2, 12, 12, 24, 0.3, dense(44, 1.5))]}, 4),
+    # a model whose config names neither the convolution nor a mask: plain causal attention, no state at all
+    "f": ({"architecture": "Sulepel", "vocab": 90, "width": 48, "norm": {"eps": 1e-5, "groups": 2},
+           "layers": [{"type": "attention", "mixer": {"heads": 3, "kv_heads": 1, "dim": 16, "vdim": 16, "scale": 0.25},
+                       "mlp": dense(64, 2.0)},
+                      latent(3, 16, 16, 32, 0.25, dense(64, 2.0))]}, 8),
 }
-LENGTHS = {"a": (23, 47, 75, 141), "b": (9, 70, 35, 101), "c": (40, 130, 301, 215), "d": (12, 66, 31, 90), "e": (7, 45, 29, 70)}
-PROMPTS = {"a": (3, 30, 41, 100), "b": (1, 64, 2, 67), "c": (8, 128, 260, 101), "d": (2, 40, 30, 51), "e": (2, 33, 20, 40)}
+LENGTHS = {"a": (23, 47, 75, 141), "b": (9, 70, 35, 101), "c": (40, 130, 301, 215), "d": (12, 66, 31, 90), "e": (7, 45, 29, 70), "f": (5, 40, 18, 77)}
+PROMPTS = {"a": (3, 30, 41, 100), "b": (1, 64, 2, 67), "c": (8, 128, 260, 101), "d": (2, 40, 30, 51), "e": (2, 33, 20, 40), "f": (3, 20, 10, 50)}
 
 
 def write_folder(folder, cfg, weights, dtype):

@@ -25,7 +25,7 @@ def test_config_is_read_key_by_key():
     assert c.layers[0].mixer.chunk == 12 and c.layers[0].feed_forward.limit == 2.0
     assert c.layers[1].mixer.kv_rank == 40 and c.layers[1].feed_forward is None
     for path, value, word in ((("width",), None, "width"), (("norm", "groups"), None, "groups"),
-                              (("canon", "taps"), None, "taps"), (("layers", 0, "mixer", "mask"), None, "mask"),
+                              (("canon", "taps"), None, "taps"), (("layers", 0, "mixer", "mask", "size"), None, "size"),
                               (("layers", 0, "mixer", "scale"), None, "scale"), (("layers", 1, "mixer", "kv_rank"), None, "kv_rank"),
                               (("layers", 0, "type"), "sliding", "sliding"), (("layers", 0, "mlp", "kind"), "routed", "routed"),
                               (("norm", "groups"), 5, "groups"), (("layers", 0, "mixer", "kv_heads"), 3, "kv_heads")):
@@ -50,6 +50,16 @@ def test_description_and_cache_plan():
     assert [tuple(s.shape) for s in model.states] == [(2, 48), (2, 48)]          # taps - 1 inputs per layer and request
     assert [r.extra_states for r in model.runs] == [(("mixer_input", 0),), (("mixer_input", 1),)]
     assert 16 in model.tile_sizes
+
+
+def test_a_config_without_convolution_or_mask_describes_a_model_without_them():
+    bare = copy.deepcopy(CFG)
+    del bare["canon"]
+    del bare["layers"][0]["mixer"]["mask"]
+    model = Model(spec_for(bare))
+    assert {d.name: tuple(d.shape) for d in model.tensors()} == ps.tensor_shapes(bare)
+    assert not any(d.name.endswith("canon1") for d in model.tensors()) and model.states == []
+    assert [(g.window, g.chunk) for g in model.groups] == [(None, None), (None, None)]
 
 
 def test_cache_manager_gives_back_pages_before_the_current_chunk():
