@@ -165,6 +165,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // Gated activations of a fused gate/up product, act(g, u), in 32 bits:
 //   kind 0: silu(g) * u
 //   kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit); g' * sigmoid(slope * g') * (u' + 1)
+//   kind 2: max(g, 0) * u
 struct GatedActivation {
   int kind = 0;
   float slope = 1.0f;
@@ -178,6 +179,7 @@ __device__ __forceinline__ float gated_activation(float g, float u, const GatedA
     if constexpr (FAST_EXP) return __fdividef(g, 1.0f + __expf(-a.slope * g)) * u;
     return g / (1.0f + expf(-a.slope * g)) * u;
   }
+  if (a.kind == 2) return fmaxf(g, 0.0f) * u;
   if constexpr (FAST_EXP) return __fdividef(g, 1.0f + __expf(-g)) * u;
   return g / (1.0f + expf(-g)) * u;
 }

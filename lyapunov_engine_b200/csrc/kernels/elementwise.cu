@@ -216,7 +216,7 @@ LE_API int le_embed_sinusoid(float *out, const void *table, int table_dtype, con
 LE_API int le_glu(void *out, const void *gate_up, int dtype, int num_tokens, int inter, int kind, float alpha, float limit,
                   cudaStream_t stream) {
   if (num_tokens <= 0) return 0;
-  if (kind != 0 && kind != 1) return le::invalid("le_glu: unknown activation %d", kind);
+  if (kind < 0 || kind > 2) return le::invalid("le_glu: unknown activation %d", kind);
   const int64_t total = static_cast<int64_t>(num_tokens) * inter;
   const int threads = 256;
   const int64_t blocks = (total + threads - 1) / threads;

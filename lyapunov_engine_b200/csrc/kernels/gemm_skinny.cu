@@ -444,7 +444,7 @@ LE_API int le_gemm_skinny_bf16(void *out, int out_dtype, const void *x, const vo
   if (splits < 1 || splits > 65535) return le::invalid("le_gemm_skinny_bf16: %d splits", splits);
   if (gated) {
     if (splits != 1 || out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_skinny_bf16: the gated form has one split, bfloat16 output and an even N");
-    if (act_kind != 0 && act_kind != 1) return le::invalid("le_gemm_skinny_bf16: unknown activation %d", act_kind);
+    if (act_kind < 0 || act_kind > 2) return le::invalid("le_gemm_skinny_bf16: unknown activation %d", act_kind);
     return dispatch_m<true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, 1, 0, stream, le::GatedActivation{act_kind, act_slope, act_limit});
   }
   if (splits > 1 && out_dtype != LE_F32) return le::invalid("le_gemm_skinny_bf16: partial sums of a split K are float32");

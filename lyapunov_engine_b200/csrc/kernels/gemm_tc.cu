@@ -399,7 +399,7 @@ LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *
                            int64_t ldo, int gated, int act_kind, float act_slope, float act_limit, int *status,
                            cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (act_kind != 0 && act_kind != 1) return le::invalid("le_gemm_tc_bf16: unknown activation %d", act_kind);
+  if (act_kind < 0 || act_kind > 2) return le::invalid("le_gemm_tc_bf16: unknown activation %d", act_kind);
   const le::GatedActivation act{act_kind, act_slope, act_limit};
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_tc_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return le::invalid("le_gemm_tc_bf16: x and W must be 16-byte aligned");

@@ -1,0 +1,293 @@
+// Routed experts: the router, the grouping of (token, choice) pairs by expert,
+// the products over those groups, and the weighted sum.
+//
+// route:   z = Wr h + b in 32 bits (Wr, b float32; h in the activations'
+//          type), the `top` largest z (ties: the lower index), their weights
+//          softmax over the chosen z only; and, where given, one more number
+//          per token, sigmoid(sg . h), for a shared expert.  One warp a token.
+// group:   pair p = t * top + j goes to expert id[p].  Counting sort in one
+//          block: offsets per expert, the pairs in expert order, and a list of
+//          row tiles (expert, first sorted slot, rows), each tile within one
+//          expert.  The order of an expert's pairs is arbitrary; no result
+//          depends on it, every row of a product is computed by itself.
+// grouped: C[row] = A[src(row)] W[expert]^T over the tiles, FP32 pipes, inputs
+//          float32 or bfloat16, sums in ascending k in float32.  Gated form:
+//          W[expert] is [2 F, K] (gate rows, then up rows) and C = act(gate,
+//          up), F wide.  Input rows are gathered through `src_of_slot` divided
+//          by `src_div` (pairs -> tokens) or are the sorted slots themselves;
+//          output rows go to the sorted slot or are scattered back to the pair
+//          with the pair's weight as a factor (float32 output).
+// combine: out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t]).
+#include "common.cuh"
+
+namespace {
+
+constexpr int TILE_M = 32;   // sorted slots per tile
+constexpr int TILE_N = 64;   // output columns per block
+constexpr int TILE_K = 32;
+
+template <typename T>
+__global__ void moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restrict__ w_router,
+                                 const float *__restrict__ b_router, const float *__restrict__ w_gate,
+                                 int32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate, int tokens,
+                                 int width, int experts, int top) {
+  extern __shared__ float smem[];
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * warps + warp;
+  if (t >= tokens) return;
+  float *z = smem + warp * experts;
+  const T *x = h + static_cast<int64_t>(t) * h_stride;
+  for (int e = 0; e < experts; ++e) {
+    const float *w = w_router + static_cast<int64_t>(e) * width;
+    float acc = 0.0f;
+    for (int c = lane; c < width; c += 32) acc = fmaf(le::to_f32(x[c]), w[c], acc);
+    acc = le::warp_sum(acc);
+    if (lane == 0) z[e] = acc + (b_router != nullptr ? b_router[e] : 0.0f);
+  }
+  if (w_gate != nullptr) {
+    float acc = 0.0f;
+    for (int c = lane; c < width; c += 32) acc = fmaf(le::to_f32(x[c]), w_gate[c], acc);
+    acc = le::warp_sum(acc);
+    if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-acc));
+  }
+  __syncwarp();
+  float first = 0.0f, total = 0.0f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ov > best || (ov == best && oa < at)) { best = ov; at = oa; }
+    }
+    if (at == 0x7fffffff) at = 0;   // (no finite logit left: cannot happen with top <= experts)
+    if (j == 0) first = best;
+    const float p = expf(best - first);
+    total += p;
+    if (lane == 0) {
+      ids[static_cast<int64_t>(t) * top + j] = at;
+      weights[static_cast<int64_t>(t) * top + j] = p;
+      z[at] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  for (int j = lane; j < top; j += 32) weights[static_cast<int64_t>(t) * top + j] /= total;
+}
+
+// One block.  meta[0] = number of tiles.
+__global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int32_t *__restrict__ slot_pair,
+                                 int32_t *__restrict__ tile_expert, int32_t *__restrict__ tile_first,
+                                 int32_t *__restrict__ tile_rows, int32_t *__restrict__ meta) {
+  extern __shared__ int32_t ism[];
+  int32_t *count = ism;                 // [experts]
+  int32_t *offset = ism + experts;      // [experts + 1]
+  int32_t *tile_at = offset + experts + 1;  // [experts + 1]
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0, tiles = 0;
+    for (int e = 0; e < experts; ++e) {
+      offset[e] = acc;
+      tile_at[e] = tiles;
+      acc += count[e];
+      tiles += (count[e] + TILE_M - 1) / TILE_M;
+    }
+    offset[experts] = acc;
+    tile_at[experts] = tiles;
+    meta[0] = tiles;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int n = count[e];
+    for (int i = 0, k = tile_at[e]; i < n; i += TILE_M, ++k) {
+      tile_expert[k] = e;
+      tile_first[k] = offset[e] + i;
+      tile_rows[k] = n - i < TILE_M ? n - i : TILE_M;
+    }
+    count[e] = 0;       // reused as the fill pointer
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    const int e = ids[p];
+    if (e >= 0 && e < experts) slot_pair[offset[e] + atomicAdd(&count[e], 1)] = p;
+  }
+}
+
+template <typename T, typename TOut, bool GATED>
+__global__ void moe_grouped_kernel(TOut *__restrict__ out, int64_t out_stride, const T *__restrict__ a, int64_t a_stride,
+                                   const T *__restrict__ w, int64_t expert_stride, int64_t w_stride,
+                                   const int32_t *__restrict__ slot_pair, int src_div, int scatter,
+                                   const float *__restrict__ pair_weight, const int32_t *__restrict__ tile_expert,
+                                   const int32_t *__restrict__ tile_first, const int32_t *__restrict__ tile_rows,
+                                   const int32_t *__restrict__ meta, int N, int K, le::GatedActivation act) {
+  __shared__ float a_s[TILE_K][TILE_M + 1];
+  __shared__ float w_s[GATED ? 2 : 1][TILE_K][TILE_N + 1];
+  __shared__ int32_t src_row[TILE_M], dst_row[TILE_M];
+  __shared__ float row_factor[TILE_M];
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int expert = tile_expert[tile], first = tile_first[tile], rows = tile_rows[tile];
+  const int n0 = blockIdx.x * TILE_N;
+  if (threadIdx.x < TILE_M) {
+    const int i = threadIdx.x;
+    int src = 0, dst = 0;
+    float f = 1.0f;
+    if (i < rows) {
+      const int pair = slot_pair[first + i];
+      src = src_div > 0 ? pair / src_div : first + i;
+      dst = scatter ? pair : first + i;
+      if (pair_weight != nullptr) f = pair_weight[pair];
+    }
+    src_row[i] = src;
+    dst_row[i] = dst;
+    row_factor[i] = f;
+  }
+  __syncthreads();
+  const T *w_e = w + static_cast<int64_t>(expert) * expert_stride;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;       // 16 x 16 threads: 2 rows x 4 columns each
+  float acc[2][4] = {}, acc_up[2][4] = {};
+  for (int k0 = 0; k0 < K; k0 += TILE_K) {
+    for (int i = threadIdx.x; i < TILE_M * TILE_K; i += blockDim.x) {
+      const int m = i / TILE_K, k = i - m * TILE_K;
+      a_s[k][m] = (m < rows && k0 + k < K) ? le::to_f32(a[static_cast<int64_t>(src_row[m]) * a_stride + k0 + k]) : 0.0f;
+    }
+    for (int i = threadIdx.x; i < TILE_N * TILE_K; i += blockDim.x) {
+      const int n = i / TILE_K, k = i - n * TILE_K;
+      const bool in = n0 + n < N && k0 + k < K;
+      w_s[0][k][n] = in ? le::to_f32(w_e[static_cast<int64_t>(n0 + n) * w_stride + k0 + k]) : 0.0f;
+      if constexpr (GATED) w_s[1][k][n] = in ? le::to_f32(w_e[static_cast<int64_t>(N + n0 + n) * w_stride + k0 + k]) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < TILE_K; ++k) {
+      const float a0 = a_s[k][ty * 2], a1 = a_s[k][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = w_s[0][k][tx * 4 + j];
+        acc[0][j] = fmaf(a0, b, acc[0][j]);
+        acc[1][j] = fmaf(a1, b, acc[1][j]);
+        if constexpr (GATED) {
+          const float bu = w_s[1][k][tx * 4 + j];
+          acc_up[0][j] = fmaf(a0, bu, acc_up[0][j]);
+          acc_up[1][j] = fmaf(a1, bu, acc_up[1][j]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = ty * 2 + i;
+    if (m >= rows) continue;
+    TOut *o = out + static_cast<int64_t>(dst_row[m]) * out_stride;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= N) continue;
+      float v = acc[i][j];
+      if constexpr (GATED) v = le::gated_activation(v, acc_up[i][j], act);
+      o[n] = le::from_f32<TOut>(v * row_factor[m]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void moe_combine_kernel(T *__restrict__ out, const float *__restrict__ y, const T *__restrict__ shared_out,
+                                   const float *__restrict__ gate, int64_t n, int width, int top) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t t = i / width, c = i - t * width;
+  float acc = 0.0f;
+  for (int j = 0; j < top; ++j) acc += y[(t * top + j) * width + c];
+  if (shared_out != nullptr) acc = fmaf(gate != nullptr ? gate[t] : 1.0f, le::to_f32(shared_out[i]), acc);
+  out[i] = le::from_f32<T>(acc);
+}
+
+}  // namespace
+
+LE_API int le_moe_tile_rows() { return TILE_M; }
+
+LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float *w_router, const float *b_router,
+                        const float *w_gate, int32_t *ids, float *weights, float *gate, int tokens, int width, int experts,
+                        int top, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (top < 1 || top > experts) return le::invalid("le_moe_route: %d of %d experts", top, experts);
+  const int warps = 4;
+  const size_t smem = sizeof(float) * warps * experts;
+  if (smem > 48 * 1024) return le::invalid("le_moe_route: up to %d experts, got %d", 48 * 1024 / 16, experts);
+  const dim3 grid((tokens + warps - 1) / warps), block(warps * 32);
+  if (dtype == LE_BF16)
+    return le::launch_chained(moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream,
+                              static_cast<const __nv_bfloat16 *>(h), h_stride, w_router, b_router, w_gate, ids, weights, gate,
+                              tokens, width, experts, top);
+  return le::launch_chained(moe_route_kernel<float>, grid, block, smem, stream, static_cast<const float *>(h), h_stride,
+                            w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top);
+}
+
+LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int32_t *slot_pair, int32_t *tile_expert,
+                        int32_t *tile_first, int32_t *tile_rows, int32_t *meta, cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  const size_t smem = sizeof(int32_t) * (3 * experts + 2);
+  if (smem > 48 * 1024) return le::invalid("le_moe_group: too many experts (%d)", experts);
+  return le::launch_chained(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, pairs, experts, slot_pair, tile_expert,
+                            tile_first, tile_rows, meta);
+}
+
+// `max_tiles`: what the grid is sized for, pairs / TILE_M + experts at most.
+LE_API int le_moe_grouped(void *out, int out_dtype, int64_t out_stride, const void *a, int64_t a_stride, const void *w,
+                          int64_t expert_stride, int64_t w_stride, int dtype, const int32_t *slot_pair, int src_div,
+                          int scatter, const float *pair_weight, const int32_t *tile_expert, const int32_t *tile_first,
+                          const int32_t *tile_rows, const int32_t *meta, int max_tiles, int N, int K, int gated, int act_kind,
+                          float act_slope, float act_limit, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (max_tiles > 65535) return le::invalid("le_moe_grouped: %d row tiles are more than a grid holds", max_tiles);
+  le::GatedActivation act;
+  act.kind = act_kind;
+  act.slope = act_slope;
+  act.limit = act_limit;
+  const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles), block(256);
+#define LE_MOE_LAUNCH(T, TOut, GATED)                                                                                         \
+  return le::launch_chained(moe_grouped_kernel<T, TOut, GATED>, grid, block, 0, stream, static_cast<TOut *>(out), out_stride, \
+                            static_cast<const T *>(a), a_stride, static_cast<const T *>(w), expert_stride, w_stride,          \
+                            slot_pair, src_div, scatter, pair_weight, tile_expert, tile_first, tile_rows, meta, N, K, act)
+  if (dtype == LE_BF16) {
+    if (gated && out_dtype == LE_BF16) LE_MOE_LAUNCH(__nv_bfloat16, __nv_bfloat16, true);
+    if (!gated && out_dtype == LE_F32) LE_MOE_LAUNCH(__nv_bfloat16, float, false);
+    if (!gated && out_dtype == LE_BF16) LE_MOE_LAUNCH(__nv_bfloat16, __nv_bfloat16, false);
+  } else if (out_dtype == LE_F32) {
+    if (gated) LE_MOE_LAUNCH(float, float, true);
+    LE_MOE_LAUNCH(float, float, false);
+  }
+#undef LE_MOE_LAUNCH
+  return le::invalid("le_moe_grouped: no form for input type %d, output type %d, gated %d", dtype, out_dtype, gated);
+}
+
+LE_API int le_moe_combine(void *out, int dtype, const float *y, const void *shared_out, const float *gate, int tokens,
+                          int width, int top, cudaStream_t stream) {
+  const int64_t n = static_cast<int64_t>(tokens) * width;
+  if (n <= 0) return 0;
+  const dim3 grid(static_cast<unsigned>((n + 255) / 256)), block(256);
+  if (dtype == LE_BF16)
+    return le::launch_chained(moe_combine_kernel<__nv_bfloat16>, grid, block, 0, stream, static_cast<__nv_bfloat16 *>(out), y,
+                              static_cast<const __nv_bfloat16 *>(shared_out), gate, n, width, top);
+  return le::launch_chained(moe_combine_kernel<float>, grid, block, 0, stream, static_cast<float *>(out), y,
+                            static_cast<const float *>(shared_out), gate, n, width, top);
+}

@@ -127,17 +127,20 @@ class Model:
             found = self._decode_variants[key] = tuple(seen)
         return found
 
-    def forward(self, ctx, cache):
+    def forward(self, ctx, cache, observe=None):
         """Logits [wanted rows, vocab] float32 (None when nothing is wanted).
-        ``cache.binding(run_index)`` gives each run its pages and state."""
+        ``cache.binding(run_index)`` gives each run its pages and state.
+        ``observe(run_index, stream)`` is called after every run, with the
+        residual stream as the run leaves it (its last output still pending)."""
         # a request whose first tokens are in this step starts from zero state, whoever held its slot before
         cache.zero_fresh_states(ctx)
         resid = self.embedding.forward(ctx)
         stream = ResidualStream(resid)
         for index, run in enumerate(self.runs):
             self.blocks[run.layer].forward(stream, ctx, cache.binding(index))
+            if observe is not None:
+                observe(index, stream)
         if ctx.num_wanted == 0:
             return None
-        normed = self.final_norm.apply(stream.resid, stream.pending, rows=ctx.wanted_rows, workspace=ctx.workspace,
-                                       key="final_normed")
+        normed = self.final_norm.apply_stream(stream, rows=ctx.wanted_rows, workspace=ctx.workspace, key="final_normed")
         return self.head.forward(normed, ctx)

@@ -99,6 +99,23 @@ _CORE_SIGNATURES = {
                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "le_gemm_simt": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64,
                      c_void_p],
+    "le_stream_norm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
+    "le_stream_sum": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "le_rope_pairs_store": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_int, c_void_p, c_void_p],
+    "le_maps_combine": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                        c_float, c_void_p],
+    "le_softcap": [c_void_p, c_int64, c_float, c_void_p],
+    "le_moe_tile_rows": [],
+    "le_moe_route": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                     c_int, c_int, c_void_p],
+    "le_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "le_moe_grouped": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int,
+                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                       c_float, c_void_p],
+    "le_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "le_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p],
     "le_sample": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                   c_void_p, c_void_p],
@@ -257,13 +274,13 @@ def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> None:
     _check(core().le_swiglu(_ptr(out), _ptr(gate_up), dtype_code(out.dtype), T, I, _stream()), "le_swiglu")
 
 
-GLU_SILU, GLU_CLAMPED = 0, 1
+GLU_SILU, GLU_CLAMPED, GLU_RELU = 0, 1, 2
 
 
 def glu(out: torch.Tensor, gate_up: torch.Tensor, kind: int = GLU_SILU, alpha: float = 1.0, limit: float = 0.0) -> None:
     """out[t, i] from gate g = gate_up[t, i] and u = gate_up[t, I + i].
     GLU_SILU: silu(g) * u.  GLU_CLAMPED: g' = min(g, limit), u' = clamp(u,
-    -limit, limit); g' * sigmoid(alpha * g') * (u' + 1)."""
+    -limit, limit); g' * sigmoid(alpha * g') * (u' + 1).  GLU_RELU: max(g, 0) * u."""
     _need_cuda(out, gate_up)
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and out.is_contiguous() and gate_up.is_contiguous() and out.dtype == gate_up.dtype
@@ -868,3 +885,177 @@ def sample(out, logits, temperature, top_p, top_k, seeds, uniforms=None, probs_o
     assert top_k.dtype == torch.int32 and seeds.dtype == torch.int32
     _check(core().le_sample(_ptr(out), _ptr(logits), n, V, logits.stride(0), _ptr(temperature), _ptr(top_p),
                             _ptr(top_k), _ptr(seeds), _ptr(uniforms), _ptr(probs_out), _stream()), "le_sample")
+
+
+# --------------------------------------------------------------------------
+# a residual stream in several copies; rotary pairs over segmented heads; maps of a head combined; capped logits
+def stream_norm(out, streams, weight, bias, eps, delta=None, mix=None, post=None, pre=None, init=None, rows=None) -> None:
+    """One launch over a residual stream kept as S copies (``streams`` float32
+    [T, S, W]): first the pending update x'_j = sum_s mix[s, j] x_s + post[j] *
+    delta (``delta`` [T, W] in the activations' type, or float32 [P, T, W]
+    partial sums added in order; None: no update; ``init`` float32 [T, W]:
+    every copy starts as that row), written back; then u = sum_s pre[s] x'_s
+    (``pre`` None: the plain sum); then out = layer norm of u with ``weight``
+    and ``bias`` (``bias`` None: RMS norm).  ``mix`` / ``post`` None: identity /
+    ones.  With ``rows`` (int32) only those rows are read and normed, into
+    out[0 .. len(out)), and ``streams`` stays as it is."""
+    _need_cuda(out, streams, weight, bias, delta, mix, post, pre, init, rows)
+    T, S, W = streams.shape
+    n = out.shape[0]
+    assert streams.dtype == torch.float32 and streams.is_contiguous() and out.is_contiguous() and out.shape[1] == W
+    assert weight.dtype == torch.float32 and weight.numel() == W and (bias is None or (bias.dtype == torch.float32 and bias.numel() == W))
+    for v, count in ((mix, S * S), (post, S), (pre, S)):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == count)
+    parts, stride, dcode = 1, 0, dtype_code(out.dtype)
+    if delta is not None:
+        assert delta.is_contiguous() and tuple(delta.shape[-2:]) == (T, W)
+        if delta.dim() == 3:
+            assert delta.dtype == torch.float32
+            parts, stride = delta.shape[0], delta.stride(0)
+        else:
+            assert delta.dtype in (out.dtype, torch.float32)
+        dcode = dtype_code(delta.dtype)
+    if init is not None:
+        assert init.dtype == torch.float32 and init.is_contiguous() and tuple(init.shape) == (T, W)
+    if rows is not None:
+        assert rows.dtype == torch.int32 and rows.numel() >= n
+    else:
+        assert n == T
+    _check(core().le_stream_norm(_ptr(out), dtype_code(out.dtype), _ptr(streams), _ptr(init), _ptr(delta), dcode, parts,
+                                 stride, _ptr(mix), _ptr(post), _ptr(pre), _ptr(weight), _ptr(bias), _ptr(rows), float(eps),
+                                 n, W, S, _stream()), "le_stream_norm")
+
+
+def stream_sum(out, streams) -> None:
+    """out [T, W] float32 = the sum of the copies ``streams`` [T, S, W]."""
+    _need_cuda(out, streams)
+    T, S, W = streams.shape
+    assert out.shape == (T, W) and out.dtype == streams.dtype == torch.float32 and out.is_contiguous() and streams.is_contiguous()
+    _check(core().le_stream_sum(_ptr(out), _ptr(streams), T, W, S, _stream()), "le_stream_sum")
+
+
+def rope_pairs_store(q_out, src, bias, k_cache, v_cache, rates, positions, request_of_token, block_table, heads, kv_heads,
+                     segments, seg_dim, value_dim, rot, head_dim, page_size, write_kv, status) -> None:
+    """Rows of ``src`` hold queries [heads, segments, seg_dim], keys [kv_heads,
+    segments, seg_dim] and values [kv_heads, value_dim].  Adds ``bias``
+    (float32, as wide as a row, or None), turns the entries (2i, 2i + 1) below
+    ``rot`` of every segment by position * rates[i] in 32 bits, and writes
+    every (head, segment) as a query head of ``head_dim`` columns into
+    ``q_out`` (its segment at columns segment * seg_dim .., zeros elsewhere),
+    keys (a kv head's segments side by side) and values (zero-padded) into the
+    paged pools [pages, kv_heads, page, head_dim]."""
+    _need_cuda(q_out, src, bias, k_cache, v_cache, rates, positions, block_table)
+    T = src.shape[0]
+    cols = (heads + kv_heads) * segments * seg_dim + kv_heads * value_dim
+    assert src.shape[1] == cols and src.stride(1) == 1 and q_out.dtype == src.dtype and q_out.stride(1) == 1
+    assert q_out.shape == (T, heads * segments * head_dim)
+    assert rates.dtype == torch.float32 and rates.is_contiguous() and rates.numel() >= rot // 2
+    assert bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == cols)
+    assert block_table.dtype == torch.int32 and block_table.is_contiguous()
+    pages = 0
+    if write_kv:
+        assert k_cache.dtype == src.dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (kv_heads, page_size, head_dim) and v_cache.shape == k_cache.shape
+        pages = k_cache.shape[0]
+    _check(core().le_rope_pairs_store(_ptr(src), src.stride(0), dtype_code(src.dtype), _ptr(bias), _ptr(q_out),
+                                      q_out.stride(0), _ptr(k_cache) if write_kv else None,
+                                      _ptr(v_cache) if write_kv else None, _ptr(rates), _ptr(positions),
+                                      _ptr(request_of_token), _ptr(block_table), block_table.shape[1], T, heads, kv_heads,
+                                      segments, seg_dim, value_dim, rot, head_dim, page_size, pages, 1 if write_kv else 0,
+                                      _ptr(status), _stream()), "le_rope_pairs_store")
+
+
+def maps_combine(out, attn, coef, heads, segments, head_dim, value_dim, eps, post) -> None:
+    """out[t, h, :value_dim] = post * unit(sum_m coef[m] * attn[t, h * segments +
+    m, :value_dim]) with unit(o) = o / sqrt(mean(o^2) + eps) (``eps`` None: no
+    division), in 32 bits.  ``coef``: float32 [segments] on the device."""
+    _need_cuda(out, attn, coef)
+    T = attn.shape[0]
+    assert attn.shape[1] == heads * segments * head_dim and attn.stride(1) == 1 and out.shape == (T, heads * value_dim)
+    assert out.stride(1) == 1 and out.dtype == attn.dtype and coef.dtype == torch.float32 and coef.numel() == segments
+    _check(core().le_maps_combine(_ptr(out), out.stride(0), _ptr(attn), attn.stride(0), dtype_code(attn.dtype), _ptr(coef), T,
+                                  heads, segments, head_dim, value_dim, -1.0 if eps is None else float(eps), float(post),
+                                  _stream()), "le_maps_combine")
+
+
+def softcap(logits, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), float32, in place."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and cap > 0
+    _check(core().le_softcap(_ptr(logits), logits.numel(), float(cap), _stream()), "le_softcap")
+
+
+# --------------------------------------------------------------------------
+# routed experts
+_moe_tile_rows = None
+
+
+def moe_tile_rows() -> int:
+    global _moe_tile_rows
+    if _moe_tile_rows is None:
+        _moe_tile_rows = int(core().le_moe_tile_rows())
+    return _moe_tile_rows
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """Row tiles that ``pairs`` (token, choice) pairs can need at most, however they fall on the experts."""
+    return pairs // moe_tile_rows() + min(experts, pairs)
+
+
+def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int) -> None:
+    """Per row of ``h``: router logits W h + b in 32 bits, the ``top`` largest
+    (``ids`` int32 [T, top], best first), softmax over the chosen logits
+    (``weights`` float32 [T, top]); with ``w_gate`` (float32 [W]) also
+    ``gate`` [T] = sigmoid(w_gate . h)."""
+    _need_cuda(ids, weights, gate, h, w_router, b_router, w_gate)
+    T, W = h.shape
+    E = w_router.shape[0]
+    assert w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == W and h.stride(1) == 1
+    assert b_router is None or (b_router.dtype == torch.float32 and b_router.numel() == E)
+    assert ids.dtype == torch.int32 and ids.is_contiguous() and tuple(ids.shape) == (T, top)
+    assert weights.dtype == torch.float32 and weights.is_contiguous() and tuple(weights.shape) == (T, top)
+    if w_gate is not None:
+        assert w_gate.dtype == torch.float32 and w_gate.numel() == W and gate.dtype == torch.float32 and gate.numel() >= T
+    _check(core().le_moe_route(_ptr(h), h.stride(0), dtype_code(h.dtype), _ptr(w_router), _ptr(b_router), _ptr(w_gate),
+                               _ptr(ids), _ptr(weights), _ptr(gate), T, W, E, top, _stream()), "le_moe_route")
+
+
+def moe_group(ids, experts: int, slot_pair, tiles, meta) -> None:
+    """Sorts the pairs (entries of ``ids``) by expert: ``slot_pair`` int32
+    [pairs] lists the pairs expert by expert; ``tiles`` int32 [3, max tiles]
+    (expert, first slot, rows of each row tile); ``meta[0]`` the tile count."""
+    _need_cuda(ids, slot_pair, tiles, meta)
+    pairs = ids.numel()
+    assert slot_pair.dtype == tiles.dtype == meta.dtype == torch.int32 and tiles.is_contiguous() and tiles.shape[0] == 3
+    assert slot_pair.numel() >= pairs and tiles.shape[1] >= moe_max_tiles(pairs, experts)
+    _check(core().le_moe_group(_ptr(ids), pairs, experts, _ptr(slot_pair), _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]),
+                               _ptr(meta), _stream()), "le_moe_group")
+
+
+def moe_grouped(out, a, w, slot_pair, tiles, meta, max_tiles: int, src_div: int, scatter: bool, pair_weight=None,
+                gated: bool = False, activation=(0, 1.0, 0.0)) -> None:
+    """The product of every sorted slot's row with its expert's matrix
+    ``w`` [experts, N (2 F when gated), K].  Input row of a slot: row pair //
+    src_div of ``a`` (``src_div`` 0: row slot).  Output row: the slot, or with
+    ``scatter`` the pair, times ``pair_weight[pair]`` where given."""
+    _need_cuda(out, a, w, slot_pair, tiles, meta, pair_weight)
+    E, N, K = w.shape
+    if gated:
+        N //= 2
+    assert w.is_contiguous() and a.dtype == w.dtype and a.stride(1) == 1 and a.shape[1] == K and out.stride(1) == 1
+    assert out.shape[1] == N
+    _check(core().le_moe_grouped(_ptr(out), dtype_code(out.dtype), out.stride(0), _ptr(a), a.stride(0), _ptr(w), w.stride(0),
+                                 w.stride(1), dtype_code(a.dtype), _ptr(slot_pair), int(src_div), 1 if scatter else 0,
+                                 _ptr(pair_weight), _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), _ptr(meta), max_tiles, N,
+                                 K, 1 if gated else 0, int(activation[0]), float(activation[1]), float(activation[2]),
+                                 _stream()), "le_moe_grouped")
+
+
+def moe_combine(out, y, top: int, shared_out=None, gate=None) -> None:
+    """out[t] = sum_j y[t * top + j] (+ gate[t] * shared_out[t]); ``y`` float32 [T * top, W]."""
+    _need_cuda(out, y, shared_out, gate)
+    T, W = out.shape
+    assert y.dtype == torch.float32 and y.is_contiguous() and tuple(y.shape) == (T * top, W) and out.is_contiguous()
+    assert shared_out is None or (shared_out.dtype == out.dtype and shared_out.is_contiguous() and shared_out.shape == out.shape)
+    _check(core().le_moe_combine(_ptr(out), dtype_code(out.dtype), _ptr(y), _ptr(shared_out), _ptr(gate), T, W, top, _stream()),
+           "le_moe_combine")

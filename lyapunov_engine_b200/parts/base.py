@@ -104,8 +104,8 @@ class TensorDecl:
     in: "matrix" in the engine's compute type (bfloat16 or float32); "vector"
     (norm weights and the like) always 32-bit, so one stored in 32 bits stays
     exactly so; "int_table" as int32.  ``init`` is how random weights fill it:
-    "normal", "ones", "ones_jitter", "zeros" or "taps" (small numbers around
-    zero).  ``alias_of`` names the tensor
+    "normal", "ones", "ones_jitter", "zeros", "taps" (small numbers around
+    zero), "eye" (the identity matrix) or "share" (1 / count in every entry).  ``alias_of`` names the tensor
     that stands in when the checkpoint has none of this name (a tied head).
     ``std_scale``: random matrices are N(0, std * std_scale)."""
     name: str
@@ -148,6 +148,20 @@ class Part:
 class Norm(Part):
     def apply(self, resid, delta=None, rows=None):
         raise NotImplementedError
+
+    def apply_stream(self, stream, read=None, rows=None, workspace=None, key="normed"):
+        """The norm of what a sub-layer reads from ``stream`` (a
+        ``ResidualStream``), after the pending output has entered it.  A
+        stream in one copy with a plain addition pending is what every norm
+        takes; a norm that also takes a stream in several copies overrides
+        this (``read``: the reading sub-layer's ``StreamLink``; None: the sum
+        of the copies).  Without ``rows`` the pending output is consumed."""
+        if stream.copies != 1 or stream.update is not None or read is not None:
+            raise ValueError(f"{type(self).__name__} reads a residual stream in one copy only")
+        out = self.apply(stream.resid, stream.pending, rows=rows, workspace=workspace, key=key)
+        if rows is None:
+            stream.pending = None
+        return out
 
 
 class PositionEncoding(Part):
@@ -216,12 +230,18 @@ class Block(Part):
 
 class ResidualStream:
     """The 32-bit residual stream of a step and the last sub-layer's output
-    that has not been added to it yet (the next norm adds it)."""
-    __slots__ = ("resid", "pending")
+    that has not entered it yet (the next norm adds it).  ``resid`` is [T, W],
+    or [T, copies, W] where a block arrangement keeps several copies of the
+    stream; ``update`` says how ``pending`` enters: None: resid += pending;
+    else a ``StreamLink`` whose ``mix`` [copies, copies] and ``post`` [copies]
+    give copy j <- sum_s mix[s, j] copy_s + post[j] * pending."""
+    __slots__ = ("resid", "pending", "update", "copies")
 
     def __init__(self, resid, pending=None):
         self.resid = resid
         self.pending = pending
+        self.update = None
+        self.copies = 1
 
 
 # ---------------------------------------------------------------- registries

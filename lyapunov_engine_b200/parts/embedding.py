@@ -63,9 +63,12 @@ class SinusoidTokenEmbedding(TokenEmbedding):
 
 @register_head("linear_head")
 class LinearHead(Part):
-    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, tied_to: str | None = None):
+    def __init__(self, vocab_size: int, hidden_size: int, weight_name: str, tied_to: str | None = None,
+                 softcap: float | None = None):
+        """``softcap`` c: logits <- c * tanh(logits / c)."""
         self.vocab_size, self.hidden_size = int(vocab_size), int(hidden_size)
         self.weight_name, self.tied_to = weight_name, tied_to
+        self.softcap = float(softcap) if softcap else None
         self.weight = None
         self.runtime = None
 
@@ -79,4 +82,6 @@ class LinearHead(Part):
     def forward(self, normed, ctx):
         logits = ctx.workspace.get("logits", (normed.shape[0], self.vocab_size), torch.float32)
         ops.linear(logits, normed, self.weight, ctx.status)
+        if self.softcap:
+            ops.softcap(logits, self.softcap)
         return logits

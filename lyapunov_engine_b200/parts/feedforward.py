@@ -1,6 +1,7 @@
 """Gated feed-forward: down(act(gate(x), up(x))).
 
-"gated_silu" (SwiGLU): act(g, u) = silu(g) * u.  "gated_clamped": with a limit
+"gated_silu" (SwiGLU): act(g, u) = silu(g) * u.  "gated_relu": act(g, u) =
+max(g, 0) * u.  "gated_clamped": with a limit
 L and a slope a, g' = min(g, L), u' = clamp(u, -L, L), act = g' * sigmoid(a g')
 * (u' + 1).
 
@@ -45,6 +46,24 @@ class GatedFeedForward(FeedForward):
         act = ws.get("ffn_act", (T, self.intermediate_size), rt.dtype)
         ops.gated_linear(act, x, self.w_gate_up, ws, ctx.status, self.activation)
         return ops.linear_for_residual(act, self.w_down, ws, "ffn_out", ctx.status)
+
+    def forward_plain(self, x, ctx, key: str = "ffn_plain"):
+        """The same as one tensor [T, H] in the activations' type (``forward``
+        may return partial sums for the norm to add), for a caller that goes
+        on computing with it; buffers of its own, so that it can run inside
+        another feed-forward."""
+        rt = self.runtime
+        ws = ctx.workspace
+        act = ws.get(key + "_act", (x.shape[0], self.intermediate_size), rt.dtype)
+        ops.gated_linear(act, x, self.w_gate_up, ws, ctx.status, self.activation)
+        out = ws.get(key, (x.shape[0], self.hidden_size), rt.dtype)
+        ops.linear(out, act, self.w_down, ctx.status)
+        return out
+
+
+@register_feed_forward("gated_relu")
+class ReluGatedFeedForward(GatedFeedForward):
+    activation = (ops.GLU_RELU, 1.0, 0.0)
 
 
 @register_feed_forward("gated_clamped")

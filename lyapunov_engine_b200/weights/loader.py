@@ -131,6 +131,10 @@ class RandomWeights:
             t = torch.ones(d.shape, device=self.device, dtype=torch.float32)
             if d.init == "ones_jitter" and self.norm_jitter:
                 t += torch.randn(d.shape, generator=self.generator, device=self.device, dtype=torch.float32) * self.norm_jitter
+        elif d.init == "eye":
+            t = torch.eye(d.shape[0], d.shape[1], device=self.device, dtype=torch.float32)
+        elif d.init == "share":
+            t = torch.full(d.shape, 1.0 / d.shape[-1], device=self.device, dtype=torch.float32)
         elif d.init == "zeros":
             t = torch.zeros(d.shape, device=self.device, dtype=torch.float32)
         else:
