@@ -71,7 +71,7 @@ def differential_attention(h, w, p, m, eps, round_to=None):
     k = _r(h @ w[p + "k"].T + w[p + "k.b"], round_to).view(T, G, 2, d)
     v = _r(h @ w[p + "v"].T + w[p + "v.b"], round_to).view(T, G, e)
     pos = torch.arange(T)
-    rot, base = m["rot"]["dims"], m["rot"]["base"]
+    rot, base = (m["rot"]["dims"], m["rot"]["base"]) if m.get("rot") else (0, 1.0)
     q = _r(rotate_pairs(q.permute(1, 2, 0, 3), pos, rot, base), round_to)      # [H, 2, T, d]
     k = _r(rotate_pairs(k.permute(1, 2, 0, 3), pos, rot, base), round_to)      # [G, 2, T, d]
     visible = window_mask(T, m["mask"]["size"]) if m.get("mask") else window_mask(T, T)
