@@ -1023,6 +1023,258 @@ def run_sulepel(args):
     return 0
 
 
+def kaditar_config(llama: dict, window: int = 2048) -> dict:
+    """A Kaditar model with the width, layer count, vocabulary and projection sizes of the given Llama shapes: as
+    many heads, each with two maps of half the head size (the same rows of q, k, v and o; a key head in the cache is
+    as wide as Llama's), four copies of the stream, dense layers in turn with routed ones whose two
+    chosen experts and shared expert together have the dense layer's size."""
+    nh, nkv, hd, I = llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"], llama["intermediate_size"]
+    mixer = {"heads": nh, "kv_heads": nkv, "dim": hd // 2, "vdim": hd, "scale": (hd // 2) ** -0.5, "diff": 0.3,
+             "rot": {"dims": hd // 4, "base": 500000.0}, "mask": {"size": window}}
+    dense = {"kind": "dense", "ff": I}
+    routed = {"kind": "moe", "expert": {"ff": I // 4}, "router": {"experts": 16, "top": 2}, "shared": {"ff": I // 2}}
+    return {"architecture": "Kaditar", "vocab": llama["vocab_size"], "width": llama["hidden_size"], "norm": {"eps": 1e-5},
+            "streams": 4, "logit_softcap": 30.0,
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": routed if i % 2 else dense}
+                       for i in range(llama["num_hidden_layers"])]}
+
+
+def kaditar_decode_bytes(cfg, batch, context):
+    """Bytes one decode step of a Kaditar model must read: every weight it uses once (of the routed layers the shared
+    expert and at most batch * top experts), the keys and values inside every live request's window."""
+    W, V = cfg["width"], cfg["vocab"]
+    total = 2 * V * W + 8 * W
+    for layer in cfg["layers"]:
+        m, f = layer["mixer"], layer["mlp"]
+        H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        total += 2 * ((H * 2 * d + G * 2 * d + G * e) * W + W * H * e) + 16 * W
+        total += 2 * batch * min(context, m["mask"]["size"]) * G * 2 * max(2 * d, e)
+        if f["kind"] == "dense":
+            total += 2 * 3 * f["ff"] * W
+        else:
+            used = min(f["router"]["experts"], batch * f["router"]["top"])
+            total += 2 * 3 * W * (used * f["expert"]["ff"] + f["shared"]["ff"]) + 4 * (f["router"]["experts"] + 1) * W
+    return total
+
+
+def kaditar_prefill_flops(cfg, tokens):
+    """As computed here: scores over keys that hold both maps side by side (twice the needed width)."""
+    W, V = cfg["width"], cfg["vocab"]
+    flops = 2 * V * W
+    for layer in cfg["layers"]:
+        m, f = layer["mixer"], layer["mlp"]
+        H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        w = m["mask"]["size"]
+        seen = sum(min(t + 1, w) for t in range(tokens))
+        flops += 2 * tokens * ((H * 2 * d + G * 2 * d + G * e) * W + W * H * e) + 4 * (2 * H) * max(2 * d, e) * seen
+        if f["kind"] == "dense":
+            flops += 2 * tokens * 3 * f["ff"] * W
+        else:
+            flops += 2 * tokens * (3 * W * (f["router"]["top"] * f["expert"]["ff"] + f["shared"]["ff"]) + (f["router"]["experts"] + 1) * W)
+    return flops
+
+
+def kaditar_kernel_rows(pk, llama):
+    """Each kernel the design adds, alone, beside the like kernel of the Llama path at the same sizes: microseconds
+    per launch inside a captured graph over rotating tensors, the share of the measured copy bandwidth that the bytes
+    it must move make, and for the products the share of the measured bfloat16 rate."""
+    import torch
+
+    from lyapunov_engine_b200 import ops
+    from lyapunov_engine_b200.engine.runtime import Workspace
+
+    dev, bf = "cuda:0", torch.bfloat16
+    cfg = kaditar_config(llama)
+    W, nh, nkv, hd, I = llama["hidden_size"], llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"], llama["intermediate_size"]
+    m = cfg["layers"][0]["mixer"]
+    H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    khd = max(2 * d, e)
+    moe = cfg["layers"][1]["mlp"]
+    E, top, F = moe["router"]["experts"], moe["router"]["top"], moe["expert"]["ff"]
+    page = BLOCK_SIZE
+    rows = []
+
+    def median_us(launch, sets):
+        n = max(sets, 16)
+        for i in range(n):
+            launch(i % sets)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(n):
+                launch(i % sets)
+        for _ in range(3):
+            graph.replay()
+        events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(15)]
+        torch.cuda.synchronize()
+        for a, b in events:
+            a.record()
+            graph.replay()
+            b.record()
+        torch.cuda.synchronize()
+        times = sorted(a.elapsed_time(b) * 1e3 / n for a, b in events)
+        return times[len(times) // 2]
+
+    def row(kernel, like, tokens, nbytes, launch, sets, flops=0):
+        us = median_us(launch, sets)
+        r = {"kernel": kernel, "like": like, "tokens": tokens, "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
+             "hbm_frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+        if flops:
+            r["tflops"] = round(flops / us / 1e6, 1)
+            r["bf16_frac"] = round(flops / us / 1e6 / pk["bf16_tflops"], 3)
+        rows.append(r)
+
+    def sets_for(nbytes):
+        return max(2, min(64, (256 << 20) // max(nbytes, 1) + 1))
+
+    status = ops.new_status(dev)
+    ws = Workspace(dev)
+    for T in (8, 2048):
+        S = cfg["streams"]
+        nbytes = T * W * (8 * S + 2 + 2) + 8 * W
+        n = sets_for(nbytes)
+        copies = [torch.randn(T, S, W, device=dev) for _ in range(n)]
+        delta = [torch.randn(T, W, device=dev).to(bf) for _ in range(n)]
+        out = [torch.empty(T, W, device=dev, dtype=bf) for _ in range(n)]
+        weight, bias = torch.ones(W, device=dev), torch.zeros(W, device=dev)
+        mix, post, pre = torch.eye(S, device=dev).contiguous(), torch.ones(S, device=dev), torch.full((S,), 1.0 / S, device=dev)
+        row(f"stream of {S} copies: update + read + layer norm", "rmsnorm + residual", T, nbytes,
+            lambda i: ops.stream_norm(out[i], copies[i], weight, bias, 1e-5, delta=delta[i], mix=mix, post=post, pre=pre), n)
+        resid = [c[:, 0].contiguous() for c in copies]
+        row("rmsnorm + residual", "", T, T * W * 12 + 4 * W, lambda i: ops.rmsnorm(out[i], resid[i], delta[i], weight, 1e-5), n)
+        # rotary pairs + bias + spread queries + cache write, beside the rotary write of the Llama path
+        cols = (H + G) * 2 * d + G * e
+        nbytes = T * 2 * (cols + 2 * H * khd + 2 * G * khd) + 4 * cols
+        n = sets_for(nbytes)
+        pages = (T + page - 1) // page
+        src = [torch.randn(T, cols, device=dev).to(bf) for _ in range(n)]
+        qw = [torch.empty(T, 2 * H * khd, device=dev, dtype=bf) for _ in range(n)]
+        kc = torch.zeros(pages + 1, G, page, khd, device=dev, dtype=bf)
+        vc = torch.zeros_like(kc)
+        b_ = torch.zeros(cols, device=dev)
+        rates = torch.rand(m["rot"]["dims"] // 2, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev)
+        req = torch.zeros(T, dtype=torch.int32, device=dev)
+        table = torch.arange(pages, dtype=torch.int32, device=dev)[None, :].contiguous()
+        row("rotary pairs + bias + spread queries + cache write", "rotary + cache write", T, nbytes,
+            lambda i: ops.rope_pairs_store(qw[i], src[i], b_, kc, vc, rates, pos, req, table, H, G, 2, d, e, m["rot"]["dims"],
+                                           khd, page, True, status), n)
+        qkv = [torch.randn(T, (nh + 2 * nkv) * hd, device=dev).to(bf) for _ in range(n)]
+        kc2 = torch.zeros(pages + 1, nkv, page, hd, device=dev, dtype=bf)
+        vc2 = torch.zeros_like(kc2)
+        cos_sin = torch.rand(T + 1, hd, device=dev)
+        row("rotary + cache write", "", T, T * 2 * ((nh + 2 * nkv) * hd + (nh + 2 * nkv) * hd), 
+            lambda i: ops.rope_kv_write(qkv[i], kc2, vc2, cos_sin, pos, req, table, nh, nkv, hd, page, True, status), n)
+        # the maps of a head combined
+        nbytes = T * 2 * (2 * H * khd + H * e)
+        n = sets_for(nbytes)
+        attn = [torch.randn(T, 2 * H * khd, device=dev).to(bf) for _ in range(n)]
+        comb = [torch.empty(T, H * e, device=dev, dtype=bf) for _ in range(n)]
+        coef = torch.tensor([1.0, -0.5], device=dev)
+        row("two maps combined + unit norm per head", "", T, nbytes,
+            lambda i: ops.maps_combine(comb[i], attn[i], coef, H, 2, khd, e, 1e-5, 0.7), n)
+        # routed experts, step by step
+        x = [torch.randn(T, W, device=dev).to(bf) for _ in range(4)]
+        wr, br, sg = torch.randn(E, W, device=dev) * 0.05, torch.zeros(E, device=dev), torch.randn(W, device=dev) * 0.02
+        ids = torch.zeros(T, top, dtype=torch.int32, device=dev)
+        share = torch.zeros(T, top, device=dev)
+        gate = torch.zeros(T, device=dev)
+        row("router: logits, top, softmax, shared gate", "", T, T * W * 2 + 4 * (E + 1) * W,
+            lambda i: ops.moe_route(ids, share, gate, x[i % 4], wr, br, sg, top), 4)
+        pairs = T * top
+        wide = ops.moe_wide_tiles(pairs, E, bf, W, F)
+        max_tiles = ops.moe_max_tiles(pairs, E, wide)
+        slots = torch.zeros(pairs, dtype=torch.int32, device=dev)
+        tiles = torch.zeros(3, max_tiles, dtype=torch.int32, device=dev)
+        meta = torch.zeros(4, dtype=torch.int32, device=dev)
+        row("pairs grouped by expert", "", T, pairs * 8, lambda i: ops.moe_group(ids, E, slots, tiles, meta, wide), 2)
+        wgu = torch.randn(E, 2 * F, W, device=dev).to(bf) * 0.02
+        wd = torch.randn(E, W, F, device=dev).to(bf) * 0.02
+        act = torch.empty(pairs, F, device=dev, dtype=bf)
+        y = torch.empty(pairs, W, device=dev)
+        used = min(E, pairs)
+        row("experts' gate/up product, silu", "gate/up product, silu", T, 2 * (used * 2 * F * W + T * W + pairs * F),
+            lambda i: ops.moe_grouped(act, x[i % 4], wgu, slots, tiles, meta, max_tiles, src_div=top, scatter=False, gated=True, wide=wide), 4,
+            flops=2 * pairs * 2 * F * W)
+        row("experts' down product, weighted", "down product", T, 2 * (used * F * W + pairs * F) + 4 * pairs * W,
+            lambda i: ops.moe_grouped(y, act, wd, slots, tiles, meta, max_tiles, src_div=0, scatter=True, pair_weight=share.view(-1), wide=wide), 2,
+            flops=2 * pairs * F * W)
+        shared_out = torch.randn(T, W, device=dev).to(bf)
+        o2 = torch.empty(T, W, device=dev, dtype=bf)
+        row("experts' outputs summed + gated shared expert", "", T, pairs * W * 4 + T * W * 4,
+            lambda i: ops.moe_combine(o2, y, top, shared_out, gate), 2)
+        # the like products of the dense path, with the rows and sizes the chosen experts have together
+        wl = torch.randn(2 * top * F, W, device=dev).to(bf) * 0.02
+        al = torch.empty(T, top * F, device=dev, dtype=bf)
+        row("gate/up product, silu", "", T, 2 * (2 * top * F * W + T * W + T * top * F),
+            lambda i: ops.gated_linear(al, x[i % 4], wl, ws, status), 4, flops=2 * T * 2 * top * F * W)
+        wl2 = torch.randn(W, top * F, device=dev).to(bf) * 0.02
+        ol = torch.empty(T, W, device=dev, dtype=bf)
+        row("down product", "", T, 2 * (top * F * W + T * top * F + T * W), lambda i: ops.linear(ol, al, wl2, status), 2,
+            flops=2 * T * top * F * W)
+    V = llama["vocab_size"]
+    logits = torch.randn(8, V, device=dev)
+    row("capped logits", "", 8, 8 * V * 8, lambda i: ops.softcap(logits, 30.0), 2)
+    return rows
+
+
+def run_kaditar(args):
+    """--only kaditar: decode (1 and 8 requests at --context) and prefill (2,048 tokens) of a Kaditar model beside the
+    Llama model of the same width, projection sizes, layers and vocabulary (random weights, bfloat16), and the
+    design's own kernels alone beside their likes."""
+    global BLOCK_SIZE
+    import torch
+
+    BLOCK_SIZE = args.page
+    pk = peaks()
+    context = args.context or CONTEXT
+    if args.profile_step:
+        llama = dict(SHAPES[args.shapes])
+        llama["num_hidden_layers"] = args.layers or 4
+        rig = make_rig(kaditar_config(llama), context, 8, args.page)
+        rig.runner.use_cuda_graphs = False
+        if args.profile_step == "decode":
+            ms, _, _ = rig.timed_decode(args.batch, 2, 2, context)
+        else:
+            ms = rig.timed_prefill(args.tokens or PREFILL_TOKENS, 1, 2)
+        print(json.dumps({"only": "kaditar", "profile_step": args.profile_step, "layers": llama["num_hidden_layers"], "ms": round(ms, 3)}))
+        return 0
+    out = {"only": "kaditar", "peaks": pk["source"], "context": context, "sizes": {}}
+    for name in ([args.shapes] if args.shapes != "1b" or args.layers else ["1b", "3b"]):
+        llama = dict(SHAPES[name])
+        if args.layers:
+            llama["num_hidden_layers"] = args.layers
+        ka = kaditar_config(llama)
+        res = {}
+        for label, cfg in (("kaditar", ka), ("llama", llama)):
+            rig = make_rig(cfg, context, 8, args.page)
+            for b in (1, 8):
+                rig.timed_decode(b, 3, 2, context - 200)
+                ms, graph_steps, _ = rig.timed_decode(b, 24, 6, context)
+                nbytes = kaditar_decode_bytes(cfg, b, context - 12) if label == "kaditar" else decode_bytes(cfg, b, context - 12)
+                res[f"{label}_decode_b{b}_ms"] = round(ms, 4)
+                res[f"{label}_decode_b{b}_tokens_per_s"] = round(b * 1000.0 / ms, 1)
+                res[f"{label}_decode_b{b}_hbm_frac"] = round(nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+                res[f"{label}_decode_b{b}_graph_steps"] = graph_steps
+            ms = rig.timed_prefill(PREFILL_TOKENS, 3, 2)
+            flops = kaditar_prefill_flops(cfg, PREFILL_TOKENS) if label == "kaditar" else prefill_flops(cfg, PREFILL_TOKENS)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_ms"] = round(ms, 3)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_tokens_per_s"] = round(PREFILL_TOKENS * 1000.0 / ms, 1)
+            res[f"{label}_prefill_{PREFILL_TOKENS}_bf16_frac"] = round(flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"], 4)
+            rig.close()
+            del rig
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+        for k, v in res.items():
+            print(f"{name}  {k} = {v}", file=sys.stderr)
+    rows = kaditar_kernel_rows(pk, dict(SHAPES["1b"]))
+    for r in rows:
+        print("  ".join(f"{k}={v}" for k, v in r.items() if v != ""), file=sys.stderr)
+    out["kernels"] = rows
+    print(json.dumps(out))
+    return 0
+
+
 def main():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -1030,12 +1282,13 @@ def main():
     p.add_argument("--warmup", type=int, default=16)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
-    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels", "sulepel"], default=None,
+    p.add_argument("--only", choices=["decode", "prefill", "mixed", "serving", "kernels", "sulepel", "kaditar"], default=None,
                    help="run one kind of step and exit (for profilers and for further sizes); mixed = --batch decoding "
                         "requests beside one --tokens portion of a prompt in every step; serving = the reference's "
                         "serving benchmark (small model, prompts of 128 tokens, 32 generated: TTFT, ITL, tokens/s); "
                         "kernels = its kernel benchmark (RMSNorm and prefill attention over a grid of sizes); "
-                        "sulepel = the Sulepel design beside Llama at equal sizes (decode, prefill, its kernels alone)")
+                        "sulepel = the Sulepel design beside Llama at equal sizes (decode, prefill, its kernels alone); "
+                        "kaditar = the same for the Kaditar design")
     p.add_argument("--batch-sizes", nargs="+", type=int, default=[1, 4, 8, 16], help="with --only serving")
     p.add_argument("--shapes", choices=sorted(SHAPES), default="1b", help="with --only: layer sizes of Llama-3.2-1B, 3.2-3B or 3.1-8B")
     p.add_argument("--batch", type=int, default=8, help="batch of --only decode")
@@ -1065,6 +1318,8 @@ def main():
         return run_kernels(args)
     if args.only == "sulepel" and args.impl == "ours":
         return run_sulepel(args)
+    if args.only == "kaditar" and args.impl == "ours":
+        return run_kaditar(args)
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)

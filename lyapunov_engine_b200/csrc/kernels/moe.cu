@@ -4,7 +4,8 @@
 // route:   z = Wr h + b in 32 bits (Wr, b float32; h in the activations'
 //          type), the `top` largest z (ties: the lower index), their weights
 //          softmax over the chosen z only; and, where given, one more number
-//          per token, sigmoid(sg . h), for a shared expert.  One warp a token.
+//          per token, sigmoid(sg . h), for a shared expert.  A block takes
+//          eight tokens; each warp a row of the router for all of them.
 // group:   pair p = t * top + j goes to expert id[p].  Counting sort in one
 //          block: offsets per expert, the pairs in expert order, and a list of
 //          row tiles (expert, first sorted slot, rows), each tile within one
@@ -22,37 +23,48 @@
 
 namespace {
 
-constexpr int TILE_M = 32;   // sorted slots per tile
+constexpr int TILE_M = 32;        // sorted slots per tile
+constexpr int TILE_M_WIDE = 128;  // of the tensor-core kernel where experts have many rows each
 constexpr int TILE_N = 64;   // output columns per block
 constexpr int TILE_K = 32;
 
+constexpr int ROUTE_TOKENS = 8;   // tokens a block routes: a warp takes a row of the router for all of them
+
 template <typename T>
-__global__ void moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restrict__ w_router,
-                                 const float *__restrict__ b_router, const float *__restrict__ w_gate,
-                                 int32_t *__restrict__ ids, float *__restrict__ weights, float *__restrict__ gate, int tokens,
-                                 int width, int experts, int top) {
-  extern __shared__ float smem[];
+__global__ void __launch_bounds__(256)
+moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restrict__ w_router,
+                 const float *__restrict__ b_router, const float *__restrict__ w_gate, int32_t *__restrict__ ids,
+                 float *__restrict__ weights, float *__restrict__ gate, int tokens, int width, int experts, int top) {
+  extern __shared__ float smem[];       // z [ROUTE_TOKENS][experts + 1]
   le::let_successor_start();
   le::wait_for_predecessor();
-  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * warps + warp;
-  if (t >= tokens) return;
-  float *z = smem + warp * experts;
-  const T *x = h + static_cast<int64_t>(t) * h_stride;
-  for (int e = 0; e < experts; ++e) {
-    const float *w = w_router + static_cast<int64_t>(e) * width;
-    float acc = 0.0f;
-    for (int c = lane; c < width; c += 32) acc = fmaf(le::to_f32(x[c]), w[c], acc);
-    acc = le::warp_sum(acc);
-    if (lane == 0) z[e] = acc + (b_router != nullptr ? b_router[e] : 0.0f);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * ROUTE_TOKENS;
+  const int nt = tokens - t0 < ROUTE_TOKENS ? tokens - t0 : ROUTE_TOKENS;
+  const int ld = experts + 1;
+  const int rows = experts + (w_gate != nullptr ? 1 : 0);
+  const T *x = h + static_cast<int64_t>(t0) * h_stride;
+  for (int r = warp; r < rows; r += 8) {
+    const float *w = r < experts ? w_router + static_cast<int64_t>(r) * width : w_gate;
+    float acc[ROUTE_TOKENS] = {};
+#pragma unroll 2
+    for (int c = lane; c < width; c += 32) {
+      const float wv = w[c];
+#pragma unroll
+      for (int j = 0; j < ROUTE_TOKENS; ++j)
+        if (j < nt) acc[j] = fmaf(le::to_f32(x[j * h_stride + c]), wv, acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < ROUTE_TOKENS; ++j) {
+      const float v = le::warp_sum(acc[j]);
+      if (lane == 0) smem[j * ld + r] = v + (r < experts && b_router != nullptr ? b_router[r] : 0.0f);
+    }
   }
-  if (w_gate != nullptr) {
-    float acc = 0.0f;
-    for (int c = lane; c < width; c += 32) acc = fmaf(le::to_f32(x[c]), w_gate[c], acc);
-    acc = le::warp_sum(acc);
-    if (lane == 0) gate[t] = 1.0f / (1.0f + expf(-acc));
-  }
-  __syncwarp();
+  __syncthreads();
+  if (warp >= nt) return;
+  const int t = t0 + warp;
+  float *z = smem + warp * ld;
+  if (w_gate != nullptr && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[experts]));
   float first = 0.0f, total = 0.0f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
@@ -82,7 +94,7 @@ __global__ void moe_route_kernel(const T *__restrict__ h, int64_t h_stride, cons
 }
 
 // One block.  meta[0] = number of tiles.
-__global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int32_t *__restrict__ slot_pair,
+__global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int tile_m, int32_t *__restrict__ slot_pair,
                                  int32_t *__restrict__ tile_expert, int32_t *__restrict__ tile_first,
                                  int32_t *__restrict__ tile_rows, int32_t *__restrict__ meta) {
   extern __shared__ int32_t ism[];
@@ -104,7 +116,7 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int
       offset[e] = acc;
       tile_at[e] = tiles;
       acc += count[e];
-      tiles += (count[e] + TILE_M - 1) / TILE_M;
+      tiles += (count[e] + tile_m - 1) / tile_m;
     }
     offset[experts] = acc;
     tile_at[experts] = tiles;
@@ -113,10 +125,10 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int
   __syncthreads();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) {
     const int n = count[e];
-    for (int i = 0, k = tile_at[e]; i < n; i += TILE_M, ++k) {
+    for (int i = 0, k = tile_at[e]; i < n; i += tile_m, ++k) {
       tile_expert[k] = e;
       tile_first[k] = offset[e] + i;
-      tile_rows[k] = n - i < TILE_M ? n - i : TILE_M;
+      tile_rows[k] = n - i < tile_m ? n - i : tile_m;
     }
     count[e] = 0;       // reused as the fill pointer
   }
@@ -207,6 +219,147 @@ __global__ void moe_grouped_kernel(TOut *__restrict__ out, int64_t out_stride, c
   }
 }
 
+
+// ---- the same products on the tensor cores (bfloat16 inputs, mma.sync m16n8k16, float32 sums) ----
+// A block takes one row tile (TM sorted slots of one expert) and 64 output columns (gated: the 64 gate rows and the
+// 64 up rows of W that make them).  Slots are the 16-row operand, W's rows the 8-column one; a warp owns 32 slots x
+// WN columns.  K runs in steps of 32 through two cp.async stages; rows of A are gathered through the slot list, rows
+// beyond the tile and columns beyond K are filled with zeros by the copy itself.  K must be a multiple of 8 and all
+// rows 16-byte aligned.
+constexpr int MMA_TN = 64;
+constexpr int MMA_TK = 32;
+constexpr int MMA_LD = MMA_TK + 8;   // bf16 elements per shared-memory row: 80 bytes, fragment loads free of bank conflicts
+
+__device__ __forceinline__ void cp_async_16(void *smem, const void *gmem, int src_bytes) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int TM, typename TOut, bool GATED>
+__global__ void __launch_bounds__(TM == 32 ? 128 : 256)
+moe_grouped_mma_kernel(TOut *__restrict__ out, int64_t out_stride, const __nv_bfloat16 *__restrict__ a, int64_t a_stride,
+                       const __nv_bfloat16 *__restrict__ w, int64_t expert_stride, int64_t w_stride,
+                       const int32_t *__restrict__ slot_pair, int src_div, int scatter, const float *__restrict__ pair_weight,
+                       const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ tile_first,
+                       const int32_t *__restrict__ tile_rows, const int32_t *__restrict__ meta, int N, int K,
+                       le::GatedActivation act) {
+  constexpr int THREADS = TM == 32 ? 128 : 256;
+  constexpr int WARPS_M = TM / 32;                 // 1 or 4
+  constexpr int WN = TM == 32 ? 16 : 32;           // columns a warp owns
+  constexpr int NT = WN / 8;                       // its 8-column tiles
+  constexpr int WPARTS = GATED ? 2 : 1;
+  __shared__ __align__(16) __nv_bfloat16 a_s[2][TM][MMA_LD];
+  __shared__ __align__(16) __nv_bfloat16 w_s[2][WPARTS][MMA_TN][MMA_LD];
+  __shared__ int32_t src_row[TM], dst_row[TM];
+  __shared__ float row_factor[TM];
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int tile = blockIdx.y;
+  if (tile >= meta[0]) return;
+  const int expert = tile_expert[tile], first = tile_first[tile], rows = tile_rows[tile];
+  const int n0 = blockIdx.x * MMA_TN;
+  for (int i = threadIdx.x; i < TM; i += THREADS) {
+    int src = 0, dst = 0;
+    float f = 1.0f;
+    if (i < rows) {
+      const int pair = slot_pair[first + i];
+      src = src_div > 0 ? pair / src_div : first + i;
+      dst = scatter ? pair : first + i;
+      if (pair_weight != nullptr) f = pair_weight[pair];
+    }
+    src_row[i] = src;
+    dst_row[i] = dst;
+    row_factor[i] = f;
+  }
+  __syncthreads();
+  const __nv_bfloat16 *w_e = w + static_cast<int64_t>(expert) * expert_stride;
+
+  auto load_stage = [&](int stage, int k0) {
+    // 16-byte pieces: a row of a stage holds 4 of them
+    for (int i = threadIdx.x; i < TM * 4; i += THREADS) {
+      const int m = i >> 2, piece = i & 3, k = k0 + piece * 8;
+      const bool in = m < rows && k < K;
+      cp_async_16(&a_s[stage][m][piece * 8], in ? a + static_cast<int64_t>(src_row[m]) * a_stride + k : a, in ? 16 : 0);
+    }
+    for (int i = threadIdx.x; i < WPARTS * MMA_TN * 4; i += THREADS) {
+      const int part = i / (MMA_TN * 4), r = (i >> 2) % MMA_TN, piece = i & 3, k = k0 + piece * 8;
+      const bool in = n0 + r < N && k < K;
+      cp_async_16(&w_s[stage][part][r][piece * 8],
+                  in ? w_e + static_cast<int64_t>(part * N + n0 + r) * w_stride + k : w_e, in ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int wm = (warp % WARPS_M) * 32, wn = (warp / WARPS_M) * WN;
+  float acc[WPARTS][2][NT][4] = {};
+  const int steps = (K + MMA_TK - 1) / MMA_TK;
+  load_stage(0, 0);
+  for (int s = 0; s < steps; ++s) {
+    if (s + 1 < steps) {
+      load_stage((s + 1) & 1, (s + 1) * MMA_TK);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int st = s & 1;
+#pragma unroll
+    for (int kk = 0; kk < MMA_TK; kk += 16) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const __nv_bfloat16 *base = &a_s[st][wm + mt * 16][kk];
+        af[mt][0] = *reinterpret_cast<const uint32_t *>(base + (g)*MMA_LD + 2 * t4);
+        af[mt][1] = *reinterpret_cast<const uint32_t *>(base + (g + 8) * MMA_LD + 2 * t4);
+        af[mt][2] = *reinterpret_cast<const uint32_t *>(base + (g)*MMA_LD + 2 * t4 + 8);
+        af[mt][3] = *reinterpret_cast<const uint32_t *>(base + (g + 8) * MMA_LD + 2 * t4 + 8);
+      }
+#pragma unroll
+      for (int part = 0; part < WPARTS; ++part)
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const __nv_bfloat16 *base = &w_s[st][part][wn + nt * 8 + g][kk];
+          uint32_t bf[2];
+          bf[0] = *reinterpret_cast<const uint32_t *>(base + 2 * t4);
+          bf[1] = *reinterpret_cast<const uint32_t *>(base + 2 * t4 + 8);
+          mma_bf16_16816(acc[part][0][nt], af[0], bf);
+          mma_bf16_16816(acc[part][1][nt], af[1], bf);
+        }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int m = wm + mt * 16 + g + half * 8;
+      if (m >= rows) continue;
+      TOut *o = out + static_cast<int64_t>(dst_row[m]) * out_stride;
+      const float f = row_factor[m];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + wn + nt * 8 + 2 * t4 + j;
+          if (n >= N) continue;
+          float v = acc[0][mt][nt][half * 2 + j];
+          if constexpr (GATED) v = le::gated_activation(v, acc[1][mt][nt][half * 2 + j], act);
+          o[n] = le::from_f32<TOut>(v * f);
+        }
+    }
+}
+
 template <typename T>
 __global__ void moe_combine_kernel(T *__restrict__ out, const float *__restrict__ y, const T *__restrict__ shared_out,
                                    const float *__restrict__ gate, int64_t n, int width, int top) {
@@ -223,17 +376,16 @@ __global__ void moe_combine_kernel(T *__restrict__ out, const float *__restrict_
 
 }  // namespace
 
-LE_API int le_moe_tile_rows() { return TILE_M; }
+LE_API int le_moe_tile_rows(int wide) { return wide ? TILE_M_WIDE : TILE_M; }
 
 LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float *w_router, const float *b_router,
                         const float *w_gate, int32_t *ids, float *weights, float *gate, int tokens, int width, int experts,
                         int top, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (top < 1 || top > experts) return le::invalid("le_moe_route: %d of %d experts", top, experts);
-  const int warps = 4;
-  const size_t smem = sizeof(float) * warps * experts;
-  if (smem > 48 * 1024) return le::invalid("le_moe_route: up to %d experts, got %d", 48 * 1024 / 16, experts);
-  const dim3 grid((tokens + warps - 1) / warps), block(warps * 32);
+  const size_t smem = sizeof(float) * ROUTE_TOKENS * (experts + 1);
+  if (smem > 48 * 1024) return le::invalid("le_moe_route: up to %d experts, got %d", 48 * 1024 / (4 * ROUTE_TOKENS) - 1, experts);
+  const dim3 grid((tokens + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(256);
   if (dtype == LE_BF16)
     return le::launch_chained(moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream,
                               static_cast<const __nv_bfloat16 *>(h), h_stride, w_router, b_router, w_gate, ids, weights, gate,
@@ -242,27 +394,50 @@ LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float 
                             w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top);
 }
 
-LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int32_t *slot_pair, int32_t *tile_expert,
+LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int tile_m, int32_t *slot_pair, int32_t *tile_expert,
                         int32_t *tile_first, int32_t *tile_rows, int32_t *meta, cudaStream_t stream) {
   if (pairs <= 0) return 0;
+  if (tile_m != TILE_M && tile_m != TILE_M_WIDE) return le::invalid("le_moe_group: row tiles of %d or %d, got %d", TILE_M, TILE_M_WIDE, tile_m);
   const size_t smem = sizeof(int32_t) * (3 * experts + 2);
   if (smem > 48 * 1024) return le::invalid("le_moe_group: too many experts (%d)", experts);
-  return le::launch_chained(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, pairs, experts, slot_pair, tile_expert,
+  return le::launch_chained(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, pairs, experts, tile_m, slot_pair, tile_expert,
                             tile_first, tile_rows, meta);
 }
 
-// `max_tiles`: what the grid is sized for, pairs / TILE_M + experts at most.
+// `max_tiles`: what the grid is sized for, pairs / tile_m + experts at most.  `tile_m`: the row tiles' size that
+// le_moe_group was given: 32, or 128 (bfloat16 with 16-byte aligned rows only: the tensor-core form).
 LE_API int le_moe_grouped(void *out, int out_dtype, int64_t out_stride, const void *a, int64_t a_stride, const void *w,
                           int64_t expert_stride, int64_t w_stride, int dtype, const int32_t *slot_pair, int src_div,
                           int scatter, const float *pair_weight, const int32_t *tile_expert, const int32_t *tile_first,
-                          const int32_t *tile_rows, const int32_t *meta, int max_tiles, int N, int K, int gated, int act_kind,
-                          float act_slope, float act_limit, cudaStream_t stream) {
+                          const int32_t *tile_rows, const int32_t *meta, int max_tiles, int tile_m, int N, int K, int gated,
+                          int act_kind, float act_slope, float act_limit, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return 0;
   if (max_tiles > 65535) return le::invalid("le_moe_grouped: %d row tiles are more than a grid holds", max_tiles);
   le::GatedActivation act;
   act.kind = act_kind;
   act.slope = act_slope;
   act.limit = act_limit;
+  const bool aligned = K % 8 == 0 && a_stride % 8 == 0 && w_stride % 8 == 0 && expert_stride % 8 == 0 &&
+                       reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
+  if (dtype == LE_BF16 && aligned && (tile_m == TILE_M || tile_m == TILE_M_WIDE)) {
+    const dim3 mgrid((N + MMA_TN - 1) / MMA_TN, max_tiles);
+#define LE_MOE_MMA(TM, TOut, GATED)                                                                                           \
+  return le::launch_chained(moe_grouped_mma_kernel<TM, TOut, GATED>, mgrid, dim3(TM == 32 ? 128 : 256), 0, stream,            \
+                            static_cast<TOut *>(out), out_stride, static_cast<const __nv_bfloat16 *>(a), a_stride,            \
+                            static_cast<const __nv_bfloat16 *>(w), expert_stride, w_stride, slot_pair, src_div, scatter,      \
+                            pair_weight, tile_expert, tile_first, tile_rows, meta, N, K, act)
+    if (tile_m == TILE_M) {
+      if (gated && out_dtype == LE_BF16) LE_MOE_MMA(32, __nv_bfloat16, true);
+      if (!gated && out_dtype == LE_F32) LE_MOE_MMA(32, float, false);
+      if (!gated && out_dtype == LE_BF16) LE_MOE_MMA(32, __nv_bfloat16, false);
+    } else {
+      if (gated && out_dtype == LE_BF16) LE_MOE_MMA(128, __nv_bfloat16, true);
+      if (!gated && out_dtype == LE_F32) LE_MOE_MMA(128, float, false);
+      if (!gated && out_dtype == LE_BF16) LE_MOE_MMA(128, __nv_bfloat16, false);
+    }
+#undef LE_MOE_MMA
+  }
+  if (tile_m != TILE_M) return le::invalid("le_moe_grouped: the FP32-pipe form takes row tiles of %d, got %d", TILE_M, tile_m);
   const dim3 grid((N + TILE_N - 1) / TILE_N, max_tiles), block(256);
 #define LE_MOE_LAUNCH(T, TOut, GATED)                                                                                         \
   return le::launch_chained(moe_grouped_kernel<T, TOut, GATED>, grid, block, 0, stream, static_cast<TOut *>(out), out_stride, \

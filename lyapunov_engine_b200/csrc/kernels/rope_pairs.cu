@@ -87,12 +87,123 @@ __global__ void rope_pairs_store_kernel(const T *__restrict__ src, int64_t src_s
   }
 }
 
+
+// Eight consecutive elements as floats (16 bytes of bfloat16, 32 of float32).
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x;
+    v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load8(const float *p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4 *>(p), b = *reinterpret_cast<const float4 *>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16 *p, const float (&v)[8]) {
+  uint4 raw;
+  __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4 *>(p) = raw;
+}
+__device__ __forceinline__ void store8(float *p, const float (&v)[8]) {
+  *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4 *>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+// The same in pieces of eight elements (seg_dim, value_dim and every offset multiples of 8, 16-byte aligned rows): a
+// token's cosines and sines are computed once into shared memory, a thread moves 16 or 32 bytes at a time.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_pairs_store_vec_kernel(const T *__restrict__ src, int64_t src_stride, const float *__restrict__ bias,
+                            T *__restrict__ q_out, int64_t q_stride, T *__restrict__ k_cache, T *__restrict__ v_cache,
+                            const float *__restrict__ rates, const int32_t *__restrict__ positions,
+                            const int32_t *__restrict__ request_of_token, const int32_t *__restrict__ block_table,
+                            int max_blocks, int heads, int kv_heads, int segments, int seg_dim, int value_dim, int rot,
+                            int head_dim, int page_size, int num_pages, int write_kv, int *__restrict__ status) {
+  extern __shared__ float cs[];        // cos [rot / 2], sin [rot / 2]
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  const int half = rot >> 1;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(static_cast<float>(pos) * rates[i], &cs[half + i], &cs[i]);
+  __syncthreads();
+  const T *row = src + static_cast<int64_t>(t) * src_stride;
+  const int q_cols = heads * segments * seg_dim, k_cols = kv_heads * segments * seg_dim;
+
+  // eight entries of a segment from column `col` of the row, entry j0 the first: bias added, pairs below `rot` turned
+  auto turned = [&](int col, int j0, float (&v)[8]) {
+    load8(row + col + j0, v);
+    if (bias != nullptr) {
+      float b[8];
+      load8(bias + col + j0, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += b[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i += 2) {
+      const int j = j0 + i;
+      if (j + 1 < rot) {
+        const float c = cs[j >> 1], s = cs[half + (j >> 1)];
+        const float a = v[i], b = v[i + 1];
+        v[i] = a * c - b * s;
+        v[i + 1] = b * c + a * s;
+      }
+    }
+  };
+
+  T *q_row = q_out + static_cast<int64_t>(t) * q_stride;
+  const int pieces = head_dim >> 3;
+  const int q_heads = heads * segments;
+  for (int i = threadIdx.x; i < q_heads * pieces; i += blockDim.x) {
+    const int qh = i / pieces, c = (i - qh * pieces) << 3;
+    const int seg = qh % segments, j = c - seg * seg_dim;
+    float v[8] = {};
+    if (j >= 0 && j < seg_dim) turned(qh * seg_dim, j, v);
+    store8(q_row + qh * head_dim + c, v);
+  }
+  if (!write_kv) return;
+  const int b = request_of_token[t];
+  const int page = pos >= 0 ? block_table[static_cast<int64_t>(b) * max_blocks + pos / page_size] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicOr(status, LE_STATUS_BAD_PAGE);
+    return;
+  }
+  const int key_width = segments * seg_dim;
+  for (int i = threadIdx.x; i < kv_heads * pieces; i += blockDim.x) {
+    const int g = i / pieces, c = (i - g * pieces) << 3;
+    const int64_t at = ((static_cast<int64_t>(page) * kv_heads + g) * page_size + pos % page_size) * head_dim + c;
+    float k[8] = {}, v[8] = {};
+    if (c < key_width) {
+      const int seg = c / seg_dim;
+      turned(q_cols + (g * segments + seg) * seg_dim, c - seg * seg_dim, k);
+    }
+    if (c < value_dim) {
+      const int col = q_cols + k_cols + g * value_dim + c;
+      load8(row + col, v);
+      if (bias != nullptr) {
+        float bb[8];
+        load8(bias + col, bb);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] += bb[e];
+      }
+    }
+    store8(k_cache + at, k);
+    store8(v_cache + at, v);
+  }
+}
+
 // Several attention maps of a head combined into one output, in 32 bits:
 //   o = sum_m coef[m] * a_m   over the head's `segments` maps (each `head_dim`
 // wide in `attn`, of which the first value_dim columns count), then, if
 // eps >= 0, o / sqrt(mean(o^2) + eps), then times `post`.  One warp per
 // (token, head).
-template <typename T>
+template <typename T, int VEC>
 __global__ void maps_combine_kernel(T *__restrict__ out, int64_t out_stride, const T *__restrict__ attn, int64_t attn_stride,
                                     const float *__restrict__ coef, int tokens, int heads, int segments, int head_dim,
                                     int value_dim, float eps, float post) {
@@ -104,17 +215,44 @@ __global__ void maps_combine_kernel(T *__restrict__ out, int64_t out_stride, con
   const T *a = attn + static_cast<int64_t>(t) * attn_stride + static_cast<int64_t>(h) * segments * head_dim;
   T *o = out + static_cast<int64_t>(t) * out_stride + static_cast<int64_t>(h) * value_dim;
   float sq = 0.0f;
-  for (int c = lane; c < value_dim; c += 32) {
-    float v = 0.0f;
-    for (int m = 0; m < segments; ++m) v = fmaf(coef[m], le::to_f32(a[m * head_dim + c]), v);
-    sq += v * v;
+  for (int c = lane * VEC; c < value_dim; c += 32 * VEC) {
+    float v[VEC] = {};
+    for (int m = 0; m < segments; ++m) {
+      const float cm = coef[m];
+      if constexpr (VEC == 8) {
+        float x[8];
+        load8(a + m * head_dim + c, x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = fmaf(cm, x[i], v[i]);
+      } else {
+        v[0] = fmaf(cm, le::to_f32(a[m * head_dim + c]), v[0]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sq += v[i] * v[i];
   }
   sq = le::warp_sum(sq);
   const float factor = eps >= 0.0f ? rsqrtf(sq / static_cast<float>(value_dim) + eps) * post : post;
-  for (int c = lane; c < value_dim; c += 32) {
-    float v = 0.0f;
-    for (int m = 0; m < segments; ++m) v = fmaf(coef[m], le::to_f32(a[m * head_dim + c]), v);
-    o[c] = le::from_f32<T>(v * factor);
+  for (int c = lane * VEC; c < value_dim; c += 32 * VEC) {
+    float v[VEC] = {};
+    for (int m = 0; m < segments; ++m) {
+      const float cm = coef[m];
+      if constexpr (VEC == 8) {
+        float x[8];
+        load8(a + m * head_dim + c, x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = fmaf(cm, x[i], v[i]);
+      } else {
+        v[0] = fmaf(cm, le::to_f32(a[m * head_dim + c]), v[0]);
+      }
+    }
+    if constexpr (VEC == 8) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] *= factor;
+      store8(o + c, v);
+    } else {
+      o[c] = le::from_f32<T>(v[0] * factor);
+    }
   }
 }
 
@@ -136,17 +274,24 @@ LE_API int le_rope_pairs_store(const void *src, int64_t src_stride, int dtype, c
     return le::invalid("le_rope_pairs_store: %d segments of %d (rotary width %d) and values of %d do not fit heads of %d",
                        segments, seg_dim, rot, value_dim, head_dim);
   const int threads = 256;
-  if (dtype == LE_BF16)
-    return le::launch_chained(rope_pairs_store_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream,
-                              static_cast<const __nv_bfloat16 *>(src), src_stride, bias, static_cast<__nv_bfloat16 *>(q_out),
-                              q_stride, static_cast<__nv_bfloat16 *>(k_cache), static_cast<__nv_bfloat16 *>(v_cache), rates,
-                              positions, request_of_token, block_table, max_blocks, heads, kv_heads, segments, seg_dim,
-                              value_dim, rot, head_dim, page_size, num_pages, write_kv, status);
-  return le::launch_chained(rope_pairs_store_kernel<float>, dim3(tokens), dim3(threads), 0, stream,
-                            static_cast<const float *>(src), src_stride, bias, static_cast<float *>(q_out), q_stride,
-                            static_cast<float *>(k_cache), static_cast<float *>(v_cache), rates, positions, request_of_token,
-                            block_table, max_blocks, heads, kv_heads, segments, seg_dim, value_dim, rot, head_dim, page_size,
-                            num_pages, write_kv, status);
+  const int elem = dtype == LE_BF16 ? 2 : 4;
+  auto aligned = [&](const void *p) { return reinterpret_cast<uintptr_t>(p) % (8 * elem) == 0; };
+  const bool vec = seg_dim % 8 == 0 && value_dim % 8 == 0 && head_dim % 8 == 0 && src_stride % 8 == 0 && q_stride % 8 == 0 &&
+                   aligned(src) && aligned(q_out) && (!write_kv || (aligned(k_cache) && aligned(v_cache))) &&
+                   reinterpret_cast<uintptr_t>(bias) % 32 == 0;
+  const size_t smem = sizeof(float) * (rot > 0 ? rot : 2);
+#define LE_ROPE_PAIRS(KERNEL, T, SMEM)                                                                                    \
+  return le::launch_chained(KERNEL<T>, dim3(tokens), dim3(threads), SMEM, stream, static_cast<const T *>(src), src_stride, \
+                            bias, static_cast<T *>(q_out), q_stride, static_cast<T *>(k_cache), static_cast<T *>(v_cache), \
+                            rates, positions, request_of_token, block_table, max_blocks, heads, kv_heads, segments,       \
+                            seg_dim, value_dim, rot, head_dim, page_size, num_pages, write_kv, status)
+  if (dtype == LE_BF16) {
+    if (vec) LE_ROPE_PAIRS(rope_pairs_store_vec_kernel, __nv_bfloat16, smem);
+    LE_ROPE_PAIRS(rope_pairs_store_kernel, __nv_bfloat16, 0);
+  }
+  if (vec) LE_ROPE_PAIRS(rope_pairs_store_vec_kernel, float, smem);
+  LE_ROPE_PAIRS(rope_pairs_store_kernel, float, 0);
+#undef LE_ROPE_PAIRS
 }
 
 LE_API int le_maps_combine(void *out, int64_t out_stride, const void *attn, int64_t attn_stride, int dtype, const float *coef,
@@ -155,13 +300,20 @@ LE_API int le_maps_combine(void *out, int64_t out_stride, const void *attn, int6
   const int64_t warps = static_cast<int64_t>(tokens) * heads;
   if (warps <= 0) return 0;
   const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
-  if (dtype == LE_BF16)
-    return le::launch_chained(maps_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream,
-                              static_cast<__nv_bfloat16 *>(out), out_stride, static_cast<const __nv_bfloat16 *>(attn),
-                              attn_stride, coef, tokens, heads, segments, head_dim, value_dim, eps, post);
-  return le::launch_chained(maps_combine_kernel<float>, dim3(blocks), dim3(256), 0, stream, static_cast<float *>(out),
-                            out_stride, static_cast<const float *>(attn), attn_stride, coef, tokens, heads, segments, head_dim,
-                            value_dim, eps, post);
+  const int elem = dtype == LE_BF16 ? 2 : 4;
+  const bool vec = value_dim % 8 == 0 && head_dim % 8 == 0 && out_stride % 8 == 0 && attn_stride % 8 == 0 &&
+                   reinterpret_cast<uintptr_t>(out) % (8 * elem) == 0 && reinterpret_cast<uintptr_t>(attn) % (8 * elem) == 0;
+#define LE_COMBINE(T, VEC)                                                                                                   \
+  return le::launch_chained(maps_combine_kernel<T, VEC>, dim3(blocks), dim3(256), 0, stream, static_cast<T *>(out), out_stride, \
+                            static_cast<const T *>(attn), attn_stride, coef, tokens, heads, segments, head_dim, value_dim, eps, \
+                            post)
+  if (dtype == LE_BF16) {
+    if (vec) LE_COMBINE(__nv_bfloat16, 8);
+    LE_COMBINE(__nv_bfloat16, 1);
+  }
+  if (vec) LE_COMBINE(float, 8);
+  LE_COMBINE(float, 1);
+#undef LE_COMBINE
 }
 
 LE_API int le_softcap(float *x, int64_t n, float cap, cudaStream_t stream) {

@@ -21,12 +21,28 @@ namespace {
 
 constexpr int MAX_STREAMS = 8;
 
-template <typename TOut, typename TDelta>
-__global__ void stream_norm_kernel(TOut *__restrict__ out, float *__restrict__ streams, const float *__restrict__ init,
-                                   const TDelta *__restrict__ delta, int parts, int64_t part_stride,
-                                   const float *__restrict__ mix, const float *__restrict__ post,
-                                   const float *__restrict__ pre, const float *__restrict__ weight,
-                                   const float *__restrict__ bias, const int32_t *__restrict__ rows, float eps, int W, int S) {
+template <typename T, int VEC> struct Pack;
+template <> struct Pack<float, 1> { float v; __device__ float get(int) const { return v; } __device__ void set(int, float x) { v = x; } };
+template <> struct Pack<__nv_bfloat16, 1> {
+  __nv_bfloat16 v;
+  __device__ float get(int) const { return __bfloat162float(v); }
+  __device__ void set(int, float x) { v = __float2bfloat16_rn(x); }
+};
+template <> struct __align__(16) Pack<float, 4> { float v[4]; __device__ float get(int i) const { return v[i]; } __device__ void set(int i, float x) { v[i] = x; } };
+template <> struct __align__(8) Pack<__nv_bfloat16, 4> {
+  __nv_bfloat16 v[4];
+  __device__ float get(int i) const { return __bfloat162float(v[i]); }
+  __device__ void set(int i, float x) { v[i] = __float2bfloat16_rn(x); }
+};
+
+// VEC consecutive columns a thread and step (4: 16-byte accesses; the launcher sizes the block so that a row of up to
+// 2,048 columns is one step, every load of a thread in flight before its first store).
+template <typename TOut, typename TDelta, int VEC>
+__global__ void __launch_bounds__(512)
+stream_norm_kernel(TOut *__restrict__ out, float *__restrict__ streams, const float *__restrict__ init,
+                   const TDelta *__restrict__ delta, int parts, int64_t part_stride, const float *__restrict__ mix,
+                   const float *__restrict__ post, const float *__restrict__ pre, const float *__restrict__ weight,
+                   const float *__restrict__ bias, const int32_t *__restrict__ rows, float eps, int W, int S) {
   extern __shared__ float smem[];
   float *u_row = smem;               // [W]
   float *scratch = smem + W;         // [33]
@@ -43,60 +59,84 @@ __global__ void stream_norm_kernel(TOut *__restrict__ out, float *__restrict__ s
   const int64_t t = rows != nullptr ? rows[r] : r;
   const bool write_back = rows == nullptr && (delta != nullptr || init != nullptr);
   float *x_row = streams + t * S * W;
+  using F = Pack<float, VEC>;
+  using D = Pack<TDelta, VEC>;
   float sum = 0.0f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float x[MAX_STREAMS];
+  for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
+    F x[MAX_STREAMS];
     if (init != nullptr) {
-      const float v = init[t * W + c];
+      const F v = *reinterpret_cast<const F *>(init + t * W + c);
 #pragma unroll
       for (int s = 0; s < MAX_STREAMS; ++s) x[s] = v;
     } else {
 #pragma unroll
-      for (int s = 0; s < MAX_STREAMS; ++s) x[s] = s < S ? x_row[static_cast<int64_t>(s) * W + c] : 0.0f;
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < S) x[s] = *reinterpret_cast<const F *>(x_row + static_cast<int64_t>(s) * W + c);
     }
     if (delta != nullptr) {
-      float y = 0.0f;
-      for (int p = 0; p < parts; ++p) y += le::to_f32(delta[p * part_stride + t * W + c]);
-      float nx[MAX_STREAMS];
+      float y[VEC] = {};
+      for (int p = 0; p < parts; ++p) {
+        const D d = *reinterpret_cast<const D *>(delta + p * part_stride + t * W + c);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) y[i] += d.get(i);
+      }
+      F nx[MAX_STREAMS];
 #pragma unroll
       for (int j = 0; j < MAX_STREAMS; ++j) {
-        float acc = 0.0f;
         if (j < S) {
 #pragma unroll
-          for (int s = 0; s < MAX_STREAMS; ++s)
-            if (s < S) acc = fmaf(coef[s * S + j], x[s], acc);
-          acc = fmaf(coef[S * S + j], y, acc);
+          for (int i = 0; i < VEC; ++i) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+              if (s < S) acc = fmaf(coef[s * S + j], x[s].get(i), acc);
+            nx[j].set(i, fmaf(coef[S * S + j], y[i], acc));
+          }
         }
-        nx[j] = acc;
       }
 #pragma unroll
-      for (int j = 0; j < MAX_STREAMS; ++j) x[j] = nx[j];
+      for (int j = 0; j < MAX_STREAMS; ++j)
+        if (j < S) x[j] = nx[j];
     }
     if (write_back) {
 #pragma unroll
       for (int s = 0; s < MAX_STREAMS; ++s)
-        if (s < S) x_row[static_cast<int64_t>(s) * W + c] = x[s];
+        if (s < S) *reinterpret_cast<F *>(x_row + static_cast<int64_t>(s) * W + c) = x[s];
     }
-    float u = 0.0f;
 #pragma unroll
-    for (int s = 0; s < MAX_STREAMS; ++s)
-      if (s < S) u = fmaf(coef[S * S + S + s], x[s], u);
-    u_row[c] = u;
-    sum += u;
+    for (int i = 0; i < VEC; ++i) {
+      float u = 0.0f;
+#pragma unroll
+      for (int s = 0; s < MAX_STREAMS; ++s)
+        if (s < S) u = fmaf(coef[S * S + S + s], x[s].get(i), u);
+      u_row[c + i] = u;
+      sum += u;
+    }
   }
   float mean = 0.0f;
   if (bias != nullptr) mean = le::block_sum(sum, scratch) / static_cast<float>(W);
   float sq = 0.0f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    const float d = u_row[c] - mean;
-    sq += d * d;
+  for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      const float d = u_row[c + i] - mean;
+      sq += d * d;
+    }
   }
   const float inv = rsqrtf(le::block_sum(sq, scratch) / static_cast<float>(W) + eps);
   TOut *o = out + static_cast<int64_t>(r) * W;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float v = (u_row[c] - mean) * inv * weight[c];
-    if (bias != nullptr) v += bias[c];
-    o[c] = le::from_f32<TOut>(v);
+  for (int c = threadIdx.x * VEC; c < W; c += blockDim.x * VEC) {
+    const F wv = *reinterpret_cast<const F *>(weight + c);
+    F bv;
+    if (bias != nullptr) bv = *reinterpret_cast<const F *>(bias + c);
+    Pack<TOut, VEC> res;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+      float v = (u_row[c + i] - mean) * inv * wv.get(i);
+      if (bias != nullptr) v += bv.get(i);
+      res.set(i, v);
+    }
+    *reinterpret_cast<Pack<TOut, VEC> *>(o + c) = res;
   }
 }
 
@@ -116,8 +156,18 @@ int launch_stream_norm(void *out, float *streams, const float *init, const void 
                        const float *mix, const float *post, const float *pre, const float *weight, const float *bias,
                        const int32_t *rows, float eps, int n, int W, int S, cudaStream_t stream) {
   const size_t smem = sizeof(float) * (W + 33 + S * S + 2 * S);
+  auto aligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+  const bool vec = W % 4 == 0 && aligned(out) && aligned(streams) && aligned(init) && aligned(delta) && aligned(weight) &&
+                   aligned(bias) && part_stride % 4 == 0;
+  if (vec) {
+    int threads = (W / 4 + 31) / 32 * 32;
+    threads = threads > 512 ? 512 : threads;
+    return le::launch_chained(stream_norm_kernel<TOut, TDelta, 4>, dim3(n), dim3(threads), smem, stream,
+                              static_cast<TOut *>(out), streams, init, static_cast<const TDelta *>(delta), parts, part_stride,
+                              mix, post, pre, weight, bias, rows, eps, W, S);
+  }
   const int threads = W >= 1024 ? 256 : 128;
-  return le::launch_chained(stream_norm_kernel<TOut, TDelta>, dim3(n), dim3(threads), smem, stream, static_cast<TOut *>(out),
+  return le::launch_chained(stream_norm_kernel<TOut, TDelta, 1>, dim3(n), dim3(threads), smem, stream, static_cast<TOut *>(out),
                             streams, init, static_cast<const TDelta *>(delta), parts, part_stride, mix, post, pre, weight,
                             bias, rows, eps, W, S);
 }

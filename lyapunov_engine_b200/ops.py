@@ -108,13 +108,13 @@ _CORE_SIGNATURES = {
     "le_maps_combine": [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                         c_float, c_void_p],
     "le_softcap": [c_void_p, c_int64, c_float, c_void_p],
-    "le_moe_tile_rows": [],
+    "le_moe_tile_rows": [c_int],
     "le_moe_route": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                      c_int, c_int, c_void_p],
-    "le_moe_group": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "le_moe_group": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "le_moe_grouped": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int,
-                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                       c_float, c_void_p],
+                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                       c_float, c_float, c_void_p],
     "le_moe_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "le_argmax": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p],
     "le_sample": [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -987,19 +987,26 @@ def softcap(logits, cap: float) -> None:
 
 # --------------------------------------------------------------------------
 # routed experts
-_moe_tile_rows = None
+_moe_tile_rows: dict[bool, int] = {}
+MOE_WIDE_ROWS = 64      # rows an expert has on average from which the wide row tiles pay
 
 
-def moe_tile_rows() -> int:
-    global _moe_tile_rows
-    if _moe_tile_rows is None:
-        _moe_tile_rows = int(core().le_moe_tile_rows())
-    return _moe_tile_rows
+def moe_tile_rows(wide: bool = False) -> int:
+    """Sorted slots per row tile: 32, or 128 in the wide form (tensor cores, many rows per expert)."""
+    if wide not in _moe_tile_rows:
+        _moe_tile_rows[wide] = int(core().le_moe_tile_rows(1 if wide else 0))
+    return _moe_tile_rows[wide]
 
 
-def moe_max_tiles(pairs: int, experts: int) -> int:
+def moe_wide_tiles(pairs: int, experts: int, dtype, width: int, inner: int) -> bool:
+    """Whether the experts' products of ``pairs`` rows run on wide row tiles:
+    bfloat16, rows in 16-byte pieces, and enough rows per expert."""
+    return dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0 and pairs >= MOE_WIDE_ROWS * experts
+
+
+def moe_max_tiles(pairs: int, experts: int, wide: bool = False) -> int:
     """Row tiles that ``pairs`` (token, choice) pairs can need at most, however they fall on the experts."""
-    return pairs // moe_tile_rows() + min(experts, pairs)
+    return pairs // moe_tile_rows(wide) + min(experts, pairs)
 
 
 def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int) -> None:
@@ -1020,24 +1027,26 @@ def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int) -> No
                                _ptr(ids), _ptr(weights), _ptr(gate), T, W, E, top, _stream()), "le_moe_route")
 
 
-def moe_group(ids, experts: int, slot_pair, tiles, meta) -> None:
+def moe_group(ids, experts: int, slot_pair, tiles, meta, wide: bool = False) -> None:
     """Sorts the pairs (entries of ``ids``) by expert: ``slot_pair`` int32
     [pairs] lists the pairs expert by expert; ``tiles`` int32 [3, max tiles]
     (expert, first slot, rows of each row tile); ``meta[0]`` the tile count."""
     _need_cuda(ids, slot_pair, tiles, meta)
     pairs = ids.numel()
     assert slot_pair.dtype == tiles.dtype == meta.dtype == torch.int32 and tiles.is_contiguous() and tiles.shape[0] == 3
-    assert slot_pair.numel() >= pairs and tiles.shape[1] >= moe_max_tiles(pairs, experts)
-    _check(core().le_moe_group(_ptr(ids), pairs, experts, _ptr(slot_pair), _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]),
-                               _ptr(meta), _stream()), "le_moe_group")
+    assert slot_pair.numel() >= pairs and tiles.shape[1] >= moe_max_tiles(pairs, experts, wide)
+    _check(core().le_moe_group(_ptr(ids), pairs, experts, moe_tile_rows(wide), _ptr(slot_pair), _ptr(tiles[0]), _ptr(tiles[1]),
+                               _ptr(tiles[2]), _ptr(meta), _stream()), "le_moe_group")
 
 
 def moe_grouped(out, a, w, slot_pair, tiles, meta, max_tiles: int, src_div: int, scatter: bool, pair_weight=None,
-                gated: bool = False, activation=(0, 1.0, 0.0)) -> None:
+                gated: bool = False, activation=(0, 1.0, 0.0), wide: bool = False) -> None:
     """The product of every sorted slot's row with its expert's matrix
     ``w`` [experts, N (2 F when gated), K].  Input row of a slot: row pair //
     src_div of ``a`` (``src_div`` 0: row slot).  Output row: the slot, or with
-    ``scatter`` the pair, times ``pair_weight[pair]`` where given."""
+    ``scatter`` the pair, times ``pair_weight[pair]`` where given.  bfloat16
+    with rows in 16-byte pieces: tensor cores (``wide``: the tiles moe_group
+    made are the wide ones); else the FP32 pipes."""
     _need_cuda(out, a, w, slot_pair, tiles, meta, pair_weight)
     E, N, K = w.shape
     if gated:
@@ -1046,9 +1055,9 @@ def moe_grouped(out, a, w, slot_pair, tiles, meta, max_tiles: int, src_div: int,
     assert out.shape[1] == N
     _check(core().le_moe_grouped(_ptr(out), dtype_code(out.dtype), out.stride(0), _ptr(a), a.stride(0), _ptr(w), w.stride(0),
                                  w.stride(1), dtype_code(a.dtype), _ptr(slot_pair), int(src_div), 1 if scatter else 0,
-                                 _ptr(pair_weight), _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), _ptr(meta), max_tiles, N,
-                                 K, 1 if gated else 0, int(activation[0]), float(activation[1]), float(activation[2]),
-                                 _stream()), "le_moe_grouped")
+                                 _ptr(pair_weight), _ptr(tiles[0]), _ptr(tiles[1]), _ptr(tiles[2]), _ptr(meta), max_tiles,
+                                 moe_tile_rows(wide), N, K, 1 if gated else 0, int(activation[0]), float(activation[1]),
+                                 float(activation[2]), _stream()), "le_moe_grouped")
 
 
 def moe_combine(out, y, top: int, shared_out=None, gate=None) -> None:

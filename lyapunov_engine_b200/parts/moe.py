@@ -81,17 +81,18 @@ class RoutedExperts(FeedForward):
         share = ws.get("moe_share", (T, top), torch.float32)
         gate = ws.get("moe_shared_gate", (T,), torch.float32) if self.w_shared_gate is not None else None
         ops.moe_route(ids, share, gate, x, self.w_router, self.b_router, self.w_shared_gate, top)
-        max_tiles = ops.moe_max_tiles(pairs, E)
+        wide = ops.moe_wide_tiles(pairs, E, rt.dtype, W, F)
+        max_tiles = ops.moe_max_tiles(pairs, E, wide)
         slot_pair = ws.get("moe_slots", (pairs,), torch.int32)
         tiles = ws.get("moe_tiles", (3, max_tiles), torch.int32)
         meta = ws.get("moe_meta", (4,), torch.int32)
-        ops.moe_group(ids, E, slot_pair, tiles, meta)
+        ops.moe_group(ids, E, slot_pair, tiles, meta, wide)
         act = ws.get("moe_act", (pairs, F), rt.dtype)
         ops.moe_grouped(act, x, self.w_gate_up, slot_pair, tiles, meta, max_tiles, src_div=top, scatter=False, gated=True,
-                        activation=self.activation)
+                        activation=self.activation, wide=wide)
         y = ws.get("moe_y", (pairs, W), torch.float32)
         ops.moe_grouped(y, act, self.w_down, slot_pair, tiles, meta, max_tiles, src_div=0, scatter=True,
-                        pair_weight=share.view(-1))
+                        pair_weight=share.view(-1), wide=wide)
         shared_out = self.shared.forward_plain(x, ctx) if self.shared is not None else None
         out = ws.get("ffn_out", (T, W), rt.dtype)
         ops.moe_combine(out, y, top, shared_out, gate)

@@ -97,7 +97,7 @@ def models(tmp_path_factory):
         exact = {r: pk.forward(cfg, w, ids, torch.float64) for r, ids in requests.items()}
         rounded = {r: pk.forward(cfg, w, ids, torch.float64, round_to=torch.bfloat16) for r, ids in requests.items()}
         noise = float(np.sqrt(np.mean([float((rounded[r] - exact[r]).pow(2).mean()) for r in requests])))
-        out[name] = dict(cfg=cfg, page=page, w=w, folders=folders, requests=requests, exact=exact, noise=noise,
+        out[name] = dict(cfg=cfg, page=page, w=w, folders=folders, requests=requests, exact=exact, rounded=rounded, noise=noise,
                          prompt_lens={f"r{i}": n for i, n in enumerate(PROMPTS[name])})
     return out
 
@@ -113,19 +113,22 @@ def check(m, trace, dtype, out_dir, pool=None, what="", extra=()):
     if dtype == "float32":
         return ru.compare(got, ref, atol=3e-4, rtol=3e-4, what=what)
     # Sharp scores and a router's choice make rounding noise heavy-tailed: the plain implementation's own rounded run
-    # lies up to 20 units from its exact one at single places (a router logit that rounding pushes past another), with
-    # a median of 0.5 to 0.8 and under 3 % of the places above 3.  So: the median, the share of loud places, and a cap
-    # that a key wrongly seen or missed (50 units and more) still breaks.
-    units = []
+    # lies up to 20 units from its exact one at single places (a router logit that rounding pushes past another, and
+    # the places after it that see that token through their windows), with a median of 0.5 to 1.1.  So: the median, a
+    # cap that a key wrongly seen or missed (50 units and more) still breaks, and no more loud places than twice what
+    # the plain implementation's rounded run has at the same places.
+    units, own = [], []
     for (rid, p), row in sorted(got.items()):
         assert np.all(np.isfinite(row))
         d = row.astype(np.float64) - m["exact"][rid][p].numpy()
         units.append(float(np.sqrt(np.mean(d * d))) / m["noise"])
+        own.append(float((m["rounded"][rid][p] - m["exact"][rid][p]).pow(2).mean().sqrt()) / m["noise"])
     worst = int(np.argmax(units))
     assert units[worst] <= 30.0, f"{what}: place {sorted(got)[worst]}: {units[worst]:.1f} units of rounding noise"
     assert float(np.median(units)) <= 1.5, f"{what}: the median place lies {np.median(units):.2f} units of rounding noise off"
-    loud = sum(u > 4.0 for u in units)
-    assert loud <= max(2, len(units) // 20), f"{what}: {loud} of {len(units)} places above 4 units of rounding noise"
+    loud, loud_own = sum(u > 4.0 for u in units), sum(u > 4.0 for u in own)
+    assert loud <= 2 * loud_own + max(2, len(units) // 50), \
+        f"{what}: {loud} of {len(units)} places above 4 units of rounding noise (the plain rounded run: {loud_own})"
     return float(np.median(units))
 
 
@@ -187,15 +190,16 @@ def test_mixed_batches_on_a_pool_that_is_used_again(models, name, dtype, tmp_pat
     """Twice the requests, up to four live, on a pool that just holds the peak:
     late requests get pages that others gave back with their keys still in them."""
     m = models[name]
-    requests, prompts, exact = dict(m["requests"]), dict(m["prompt_lens"]), dict(m["exact"])
+    requests, prompts, exact, rounded = dict(m["requests"]), dict(m["prompt_lens"]), dict(m["exact"]), dict(m["rounded"])
     g = torch.Generator().manual_seed(11)
     for rid, ids in list(m["requests"].items()):
         requests[rid + "x"] = torch.randint(0, m["cfg"]["vocab"], (len(ids),), generator=g).tolist()
         prompts[rid + "x"] = m["prompt_lens"][rid]
         exact[rid + "x"] = pk.forward(m["cfg"], m["w"], requests[rid + "x"], torch.float64)
+        rounded[rid + "x"] = pk.forward(m["cfg"], m["w"], requests[rid + "x"], torch.float64, round_to=torch.bfloat16)
     trace = ru.mixed_trace(requests, prompts, chunk=16, max_live=4, seed=5)
     assert any(len(s["entries"]) >= 3 for s in trace.steps)
-    m2 = dict(m, requests=requests, exact=exact)
+    m2 = dict(m, requests=requests, exact=exact, rounded=rounded)
     check(m2, trace, dtype, tmp_path, pool=ru.peak_pool_tokens(trace, m["page"]), what=f"{name} {dtype} mixed",
           extra=("--max-num-seqs", "4"))
     pages = ru.read_pages(str(tmp_path))
@@ -212,6 +216,7 @@ def test_first_tokens_and_long_decoding(models, dtype, tmp_path):
     ids = torch.randint(0, m["cfg"]["vocab"], (170,), generator=g).tolist()
     other = m["requests"]["r1"]
     exact = {"long": pk.forward(m["cfg"], m["w"], ids, torch.float64), "r1": m["exact"]["r1"]}
+    rounded = {"long": pk.forward(m["cfg"], m["w"], ids, torch.float64, round_to=torch.bfloat16), "r1": m["rounded"]["r1"]}
     t = ru.Trace()
     for i, tok in enumerate(ids):
         entries = [("long", [tok], [0])]
@@ -219,7 +224,7 @@ def test_first_tokens_and_long_decoding(models, dtype, tmp_path):
         if 0 <= j < len(other):
             entries.append(("r1", [other[j]], [0]))
         t.step(entries, end=(["long"] if i == len(ids) - 1 else []) + (["r1"] if j == len(other) - 1 else []))
-    check(dict(m, exact=exact), t, dtype, tmp_path, pool=256, what=f"a {dtype} long decoding")
+    check(dict(m, exact=exact, rounded=rounded), t, dtype, tmp_path, pool=256, what=f"a {dtype} long decoding")
 
 
 def test_window_pages_are_given_back_while_a_request_lives(models, tmp_path):

@@ -225,7 +225,7 @@ def test_relu_gate_in_every_gated_kernel(dtype):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("T,W,E,top,F,shared", [(5, 64, 6, 2, 24, 40), (70, 192, 16, 2, 64, 128), (9, 100, 3, 3, 20, 0),
-                                                (33, 72, 1, 1, 16, 0), (300, 128, 40, 4, 36, 0)])
+                                                (33, 72, 1, 1, 16, 0), (300, 128, 40, 4, 36, 0), (700, 64, 4, 2, 200, 0)])
 def test_routed_experts_step_by_step(T, W, E, top, F, shared, dtype):
     """Router, grouping, both products and the weighted sum, each against plain
     arithmetic, and the whole against the plain feed-forward."""
@@ -250,28 +250,33 @@ def test_routed_experts_step_by_step(T, W, E, top, F, shared, dtype):
     torch.testing.assert_close(share.cpu(), torch.softmax(chosen.values, -1).float(), atol=1e-5, rtol=1e-5)
     torch.testing.assert_close(gate.cpu(), torch.sigmoid(h.double() @ sg.double()).float(), atol=1e-5, rtol=1e-5)
     pairs = T * top
-    max_tiles = ops.moe_max_tiles(pairs, E)
-    slots = torch.full((pairs,), -1, dtype=torch.int32, device=DEV)
-    tiles = torch.zeros(3, max_tiles, dtype=torch.int32, device=DEV)
-    meta = torch.zeros(4, dtype=torch.int32, device=DEV)
-    ops.moe_group(ids, E, slots, tiles, meta)
-    n_tiles = int(meta[0])
-    flat = ids.cpu().view(-1)
-    assert sorted(slots.cpu().tolist()) == list(range(pairs))             # every pair once
-    assert torch.equal(flat[slots.cpu().long()], flat.sort().values)      # in expert order
-    covered = []
-    for i in range(n_tiles):
-        e, first, rows = (int(tiles[j, i]) for j in range(3))
-        assert 1 <= rows <= ops.moe_tile_rows() and all(int(flat[slots[first + r]]) == e for r in range(rows))
-        covered += list(range(first, first + rows))
-    assert covered == list(range(pairs)) and n_tiles <= max_tiles
     wgu = torch.stack([torch.cat([w[f"e{e}.gate"], w[f"e{e}.up"]]) for e in range(E)]).to(dtype).to(DEV)
     wd = torch.stack([w[f"e{e}.down"] for e in range(E)]).to(dtype).to(DEV)
-    act = torch.zeros(pairs, F, dtype=dtype, device=DEV)
-    ops.moe_grouped(act, h.to(DEV), wgu, slots, tiles, meta, max_tiles, src_div=top, scatter=False, gated=True,
-                    activation=(ops.GLU_SILU, 1.0, 0.0))
-    y = torch.zeros(pairs, W, device=DEV)
-    ops.moe_grouped(y, act, wd, slots, tiles, meta, max_tiles, src_div=0, scatter=True, pair_weight=share.view(-1))
+    flat = ids.cpu().view(-1)
+    # the usual row tiles and, in bfloat16 with rows in 16-byte pieces, the wide ones of the tensor-core form
+    for wide in ((False, True) if dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0 else (False,)):
+        max_tiles = ops.moe_max_tiles(pairs, E, wide)
+        slots = torch.full((pairs,), -1, dtype=torch.int32, device=DEV)
+        tiles = torch.zeros(3, max_tiles, dtype=torch.int32, device=DEV)
+        meta = torch.zeros(4, dtype=torch.int32, device=DEV)
+        ops.moe_group(ids, E, slots, tiles, meta, wide)
+        n_tiles = int(meta[0])
+        assert sorted(slots.cpu().tolist()) == list(range(pairs))             # every pair once
+        assert torch.equal(flat[slots.cpu().long()], flat.sort().values)      # in expert order
+        covered = []
+        for i in range(n_tiles):
+            e, first, rows = (int(tiles[j, i]) for j in range(3))
+            assert 1 <= rows <= ops.moe_tile_rows(wide) and all(int(flat[slots[first + r]]) == e for r in range(rows))
+            covered += list(range(first, first + rows))
+        assert covered == list(range(pairs)) and n_tiles <= max_tiles
+        act = torch.zeros(pairs, F, dtype=dtype, device=DEV)
+        ops.moe_grouped(act, h.to(DEV), wgu, slots, tiles, meta, max_tiles, src_div=top, scatter=False, gated=True,
+                        activation=(ops.GLU_SILU, 1.0, 0.0), wide=wide)
+        y = torch.zeros(pairs, W, device=DEV)
+        ops.moe_grouped(y, act, wd, slots, tiles, meta, max_tiles, src_div=0, scatter=True, pair_weight=share.view(-1), wide=wide)
+        if wide:
+            torch.testing.assert_close(y, y_narrow, atol=2e-2, rtol=2e-2)
+        y_narrow = y
     shared_out = torch.randn(T, W, generator=g).to(dtype) if shared else None
     out = torch.zeros(T, W, dtype=dtype, device=DEV)
     ops.moe_combine(out, y, top, shared_out.to(DEV) if shared else None, gate if shared else None)
