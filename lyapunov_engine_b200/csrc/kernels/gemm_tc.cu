@@ -112,8 +112,9 @@ __device__ __forceinline__ void tile_position(int tile, int tiles_m, int tiles_n
 template <int BN, bool GATED, typename TO, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO *__restrict__ out,
-               int M, int N, int K, int64_t ldo, int up_row_offset, int tiles_m, int tiles_n, int *__restrict__ status,
-               le::GatedActivation act) {
+               int M, int N, int K, int64_t ldo, int up_row_offset, int tiles_m_most, int tiles_n, int *__restrict__ status,
+               le::GatedActivation act, const int32_t *__restrict__ tile_expert, int expert_rows,
+               const int32_t *__restrict__ tile_count) {
   static_assert(!PAIR || BN == 256, "a pair of blocks computes 256 x 256 tiles");
   constexpr int B_ROWS = PAIR ? BN / 2 : BN;         // rows of W in this block's stage
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = B_ROWS * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -130,6 +131,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_k_tiles = (K + BK - 1) / BK;
+  // Grouped form (tile_expert given): W is a stack of matrices of `expert_rows` rows each, row tile m of x is
+  // multiplied with matrix tile_expert[m], and only the first *tile_count row tiles hold rows.  Both lists come from
+  // the kernel before this one, so every role waits for it here.
+  int tiles_m = tiles_m_most;
+  if (tile_count != nullptr) {
+    le::wait_for_predecessor();
+    tiles_m = min(max(*tile_count, 0), tiles_m_most);
+  }
   const int num_tiles = tiles_m * tiles_n;
   const int rank = PAIR ? static_cast<int>(cluster_rank()) : 0;           // which block of the pair
   const int first_tile = PAIR ? blockIdx.x >> 1 : blockIdx.x;
@@ -167,7 +176,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       for (int tile = first_tile; tile < num_tiles && !*failed; tile += tile_step) {
         int m_idx, n_idx;
         tile_position(tile, tiles_m, tiles_n, m_idx, n_idx);
-        const int m0 = m_idx * TILE_ROWS + rank * BM, n0 = n_idx * N_TILE;
+        const int m0 = m_idx * TILE_ROWS + rank * BM;
+        const int n0 = n_idx * N_TILE + (tile_expert != nullptr ? tile_expert[m_idx] * expert_rows : 0);   // as a row of W
         for (int kt = 0; kt < num_k_tiles; ++kt, ++issued) {
           const int s = issued % STAGES;
           const uint32_t phase = (issued / STAGES) & 1;
@@ -329,9 +339,12 @@ bool pairs_enabled() {
   return on;
 }
 
+// Grouped form: `experts` matrices of N rows each stacked in w, `tile_expert` (device, one entry per 128 rows of x)
+// and `tile_count` (device: how many of those row tiles hold rows); M is the most rows x can hold.
 template <int BN, bool GATED, typename TO, bool PAIR = false>
 int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ldo, int *status,
-           cudaStream_t stream, const le::GatedActivation &act = le::GatedActivation{}) {
+           cudaStream_t stream, const le::GatedActivation &act = le::GatedActivation{}, int experts = 1,
+           const int32_t *tile_expert = nullptr, const int32_t *tile_count = nullptr) {
   // 192 KB of stages either way: one persistent block per SM
   constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : 6);
   constexpr int W_ROWS = PAIR ? BN / 2 : BN;             // rows of W per block and stage
@@ -341,7 +354,7 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
   CUtensorMap map_a, map_b;
   int rc = tensor_map(&map_a, x, M, K, ldx, BM);
   if (rc != 0) return rc;
-  rc = tensor_map(&map_b, w, N, K, ldw, (GATED || PAIR) ? BN / 2 : BN);
+  rc = tensor_map(&map_b, w, N * experts, K, ldw, (GATED || PAIR) ? BN / 2 : BN);
   if (rc != 0) return rc;
   auto kernel = gemm_tc_kernel<BN, GATED, TO, STAGES, PAIR>;
   cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -383,7 +396,7 @@ int launch(void *out, const void *x, const void *w, int M, int N, int K, int64_t
     config.gridDim = dim3(static_cast<int>(tiles < sms ? tiles : sms));
   }
   e = cudaLaunchKernelEx(&config, kernel, map_a, map_b, static_cast<TO *>(out), M, N, K, ldo, GATED ? N / 2 : 0, tiles_m, tiles_n,
-                         status, act);
+                         status, act, tile_expert, N, tile_count);
   if (e != cudaSuccess) return le::invalid("le_gemm_tc_bf16: launch failed: %s", cudaGetErrorString(e));
   return le::launched();
 }
@@ -431,4 +444,27 @@ LE_API int le_gemm_tc_bf16(void *out, int out_dtype, const void *x, const void *
     return wide ? launch<256, false, float>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream)
                 : launch<128, false, float>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream);
   return le::invalid("le_gemm_tc_bf16: unknown dtype code %d", out_dtype);
+}
+
+// The grouped form: x holds row tiles of 128 rows, tile m belongs to matrix tile_expert[m] of the `experts` matrices
+// [N, K] stacked in w (gated: each [2 I, K], gate rows then up rows), and the first *tile_count tiles hold rows (both on
+// the device, written by the kernel before this one).  out has x's rows.  M: the rows x has room for.
+LE_API int le_gemm_tc_grouped_bf16(void *out, int out_dtype, const void *x, const void *w, int M, int N, int K, int64_t ldx,
+                                   int64_t ldw, int64_t ldo, int experts, const int32_t *tile_expert,
+                                   const int32_t *tile_count, int gated, int act_kind, float act_slope, float act_limit,
+                                   int *status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || experts <= 0) return 0;
+  if (act_kind < 0 || act_kind > 2) return le::invalid("le_gemm_tc_grouped_bf16: unknown activation %d", act_kind);
+  const le::GatedActivation act{act_kind, act_slope, act_limit};
+  if (M % BM) return le::invalid("le_gemm_tc_grouped_bf16: x holds whole tiles of %d rows, got %d rows", BM, M);
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8) return le::invalid("le_gemm_tc_grouped_bf16: K (%d) and the leading dimensions must be multiples of 8", K);
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) & 15) return le::invalid("le_gemm_tc_grouped_bf16: x and W must be 16-byte aligned");
+  if (tile_expert == nullptr || tile_count == nullptr) return le::invalid("le_gemm_tc_grouped_bf16: the tile lists are missing");
+  if (gated) {
+    if (out_dtype != LE_BF16 || N % 2) return le::invalid("le_gemm_tc_grouped_bf16: the gated form has bfloat16 output and an even N");
+    return launch<256, true, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream, act, experts, tile_expert, tile_count);
+  }
+  if (out_dtype == LE_BF16) return launch<256, false, bf16>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream, act, experts, tile_expert, tile_count);
+  if (out_dtype == LE_F32) return launch<256, false, float>(out, x, w, M, N, K, ldx, ldw, ldo, status, stream, act, experts, tile_expert, tile_count);
+  return le::invalid("le_gemm_tc_grouped_bf16: unknown dtype code %d", out_dtype);
 }

@@ -5,7 +5,7 @@
 //          type), the `top` largest z (ties: the lower index), their weights
 //          softmax over the chosen z only; and, where given, one more number
 //          per token, sigmoid(sg . h), for a shared expert.  A block takes
-//          eight tokens; each warp a row of the router for all of them.
+//          eight tokens; each of its warps a row of the router for all of them.
 // group:   pair p = t * top + j goes to expert id[p].  Counting sort in one
 //          block: offsets per expert, the pairs in expert order, and a list of
 //          row tiles (expert, first sorted slot, rows), each tile within one
@@ -19,6 +19,10 @@
 //          output rows go to the sorted slot or are scattered back to the pair
 //          with the pair's weight as a factor (float32 output).
 // combine: out[t] = sum_j y[t * top + j] (+ gate[t] * shared[t]).
+// Where experts have many rows each (prompt portions, bfloat16) the products run on the tcgen05 kernel of
+// gemm_tc.cu in its grouped form instead: the grouping pads every expert's slots to whole tiles of 128, the rows of
+// x are gathered into slot order, both products run over the sorted rows, and the weighted sum reads them back
+// through each pair's slot.
 #include "common.cuh"
 
 namespace {
@@ -29,9 +33,21 @@ constexpr int TILE_N = 64;   // output columns per block
 constexpr int TILE_K = 32;
 
 constexpr int ROUTE_TOKENS = 8;   // tokens a block routes: a warp takes a row of the router for all of them
+constexpr int ROUTE_WARPS = 16;
+
+__device__ __forceinline__ void load4(const float *p, float (&v)[4]) {
+  const float4 a = *reinterpret_cast<const float4 *>(p);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16 *p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restrict__ w_router,
                  const float *__restrict__ b_router, const float *__restrict__ w_gate, int32_t *__restrict__ ids,
                  float *__restrict__ weights, float *__restrict__ gate, int tokens, int width, int experts, int top) {
@@ -44,15 +60,31 @@ moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restr
   const int ld = experts + 1;
   const int rows = experts + (w_gate != nullptr ? 1 : 0);
   const T *x = h + static_cast<int64_t>(t0) * h_stride;
-  for (int r = warp; r < rows; r += 8) {
+  const bool pieces = width % 4 == 0 && h_stride % 4 == 0 && reinterpret_cast<uintptr_t>(h) % 16 == 0 &&
+                      reinterpret_cast<uintptr_t>(w_router) % 16 == 0 && reinterpret_cast<uintptr_t>(w_gate) % 16 == 0;
+  for (int r = warp; r < rows; r += ROUTE_WARPS) {
     const float *w = r < experts ? w_router + static_cast<int64_t>(r) * width : w_gate;
     float acc[ROUTE_TOKENS] = {};
-#pragma unroll 2
-    for (int c = lane; c < width; c += 32) {
-      const float wv = w[c];
+    if (pieces) {
+#pragma unroll 4
+      for (int c = lane * 4; c < width; c += 128) {
+        const float4 wv = *reinterpret_cast<const float4 *>(w + c);
 #pragma unroll
-      for (int j = 0; j < ROUTE_TOKENS; ++j)
-        if (j < nt) acc[j] = fmaf(le::to_f32(x[j * h_stride + c]), wv, acc[j]);
+        for (int j = 0; j < ROUTE_TOKENS; ++j)
+          if (j < nt) {
+            float xv[4];
+            load4(x + j * h_stride + c, xv);
+            acc[j] = fmaf(xv[0], wv.x, fmaf(xv[1], wv.y, fmaf(xv[2], wv.z, fmaf(xv[3], wv.w, acc[j]))));
+          }
+      }
+    } else {
+#pragma unroll 2
+      for (int c = lane; c < width; c += 32) {
+        const float wv = w[c];
+#pragma unroll
+        for (int j = 0; j < ROUTE_TOKENS; ++j)
+          if (j < nt) acc[j] = fmaf(le::to_f32(x[j * h_stride + c]), wv, acc[j]);
+      }
     }
 #pragma unroll
     for (int j = 0; j < ROUTE_TOKENS; ++j) {
@@ -93,10 +125,14 @@ moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restr
   for (int j = lane; j < top; j += 32) weights[static_cast<int64_t>(t) * top + j] /= total;
 }
 
-// One block.  meta[0] = number of tiles.
-__global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int tile_m, int32_t *__restrict__ slot_pair,
-                                 int32_t *__restrict__ tile_expert, int32_t *__restrict__ tile_first,
-                                 int32_t *__restrict__ tile_rows, int32_t *__restrict__ meta) {
+// One block.  meta[0] = number of tiles.  `padded`: every expert's slots start at a multiple of tile_m (slots that
+// stand for no pair hold -1), so that a row tile of a product over the sorted rows lies within one expert; slots_cap
+// is what slot_pair holds then.  pair_slot (or nullptr) receives each pair's slot.
+__global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int experts, int tile_m, int padded,
+                                 int max_tiles, int slots_cap, int32_t *__restrict__ slot_pair,
+                                 int32_t *__restrict__ pair_slot, int32_t *__restrict__ tile_expert,
+                                 int32_t *__restrict__ tile_first, int32_t *__restrict__ tile_rows,
+                                 int32_t *__restrict__ meta) {
   extern __shared__ int32_t ism[];
   int32_t *count = ism;                 // [experts]
   int32_t *offset = ism + experts;      // [experts + 1]
@@ -104,6 +140,12 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int
   le::let_successor_start();
   le::wait_for_predecessor();
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  for (int k = threadIdx.x; k < max_tiles; k += blockDim.x) {
+    tile_expert[k] = 0;
+    tile_rows[k] = 0;
+  }
+  if (padded)
+    for (int i = threadIdx.x; i < slots_cap; i += blockDim.x) slot_pair[i] = -1;
   __syncthreads();
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
     const int e = ids[p];
@@ -113,12 +155,12 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int
   if (threadIdx.x == 0) {
     int acc = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
-      offset[e] = acc;
+      offset[e] = padded ? tiles * tile_m : acc;
       tile_at[e] = tiles;
       acc += count[e];
       tiles += (count[e] + tile_m - 1) / tile_m;
     }
-    offset[experts] = acc;
+    offset[experts] = padded ? tiles * tile_m : acc;
     tile_at[experts] = tiles;
     meta[0] = tiles;
   }
@@ -135,8 +177,47 @@ __global__ void moe_group_kernel(const int32_t *__restrict__ ids, int pairs, int
   __syncthreads();
   for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
     const int e = ids[p];
-    if (e >= 0 && e < experts) slot_pair[offset[e] + atomicAdd(&count[e], 1)] = p;
+    if (e >= 0 && e < experts) {
+      const int slot = offset[e] + atomicAdd(&count[e], 1);
+      slot_pair[slot] = p;
+      if (pair_slot != nullptr) pair_slot[p] = slot;
+    }
   }
+}
+
+// Rows of x gathered into slot order (16-byte pieces): out[slot] = x[slot_pair[slot] / src_div], zeros for slots that
+// stand for no pair; only the first meta[0] * tile_m slots are touched.
+template <typename T>
+__global__ void moe_gather_kernel(T *__restrict__ out, const T *__restrict__ x, int64_t x_stride,
+                                  const int32_t *__restrict__ slot_pair, int src_div, int tile_m,
+                                  const int32_t *__restrict__ meta, int width) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int slot = blockIdx.x;
+  if (slot >= meta[0] * tile_m) return;
+  const int pair = slot_pair[slot];
+  constexpr int PIECE = 16 / sizeof(T);
+  uint4 *dst = reinterpret_cast<uint4 *>(out + static_cast<int64_t>(slot) * width);
+  const uint4 *src = pair >= 0 ? reinterpret_cast<const uint4 *>(x + static_cast<int64_t>(pair / src_div) * x_stride) : nullptr;
+  for (int i = threadIdx.x; i < width / PIECE; i += blockDim.x) dst[i] = src != nullptr ? src[i] : make_uint4(0, 0, 0, 0);
+}
+
+// out[t] = sum_j share[t, j] * y[pair_slot[t * top + j]] (+ gate[t] * shared[t]): the weighted sum over rows that
+// lie in slot order.
+template <typename T, typename TY>
+__global__ void moe_combine_sorted_kernel(T *__restrict__ out, const TY *__restrict__ y, const int32_t *__restrict__ pair_slot,
+                                          const float *__restrict__ share, const T *__restrict__ shared_out,
+                                          const float *__restrict__ gate, int64_t n, int width, int top) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int64_t t = i / width, c = i - t * width;
+  float acc = 0.0f;
+  for (int j = 0; j < top; ++j)
+    acc = fmaf(share[t * top + j], le::to_f32(y[static_cast<int64_t>(pair_slot[t * top + j]) * width + c]), acc);
+  if (shared_out != nullptr) acc = fmaf(gate != nullptr ? gate[t] : 1.0f, le::to_f32(shared_out[i]), acc);
+  out[i] = le::from_f32<T>(acc);
 }
 
 template <typename T, typename TOut, bool GATED>
@@ -385,7 +466,7 @@ LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float 
   if (top < 1 || top > experts) return le::invalid("le_moe_route: %d of %d experts", top, experts);
   const size_t smem = sizeof(float) * ROUTE_TOKENS * (experts + 1);
   if (smem > 48 * 1024) return le::invalid("le_moe_route: up to %d experts, got %d", 48 * 1024 / (4 * ROUTE_TOKENS) - 1, experts);
-  const dim3 grid((tokens + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(256);
+  const dim3 grid((tokens + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(ROUTE_WARPS * 32);
   if (dtype == LE_BF16)
     return le::launch_chained(moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream,
                               static_cast<const __nv_bfloat16 *>(h), h_stride, w_router, b_router, w_gate, ids, weights, gate,
@@ -394,14 +475,51 @@ LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float 
                             w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top);
 }
 
-LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int tile_m, int32_t *slot_pair, int32_t *tile_expert,
-                        int32_t *tile_first, int32_t *tile_rows, int32_t *meta, cudaStream_t stream) {
+LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int tile_m, int padded, int max_tiles, int slots_cap,
+                        int32_t *slot_pair, int32_t *pair_slot, int32_t *tile_expert, int32_t *tile_first, int32_t *tile_rows,
+                        int32_t *meta, cudaStream_t stream) {
   if (pairs <= 0) return 0;
   if (tile_m != TILE_M && tile_m != TILE_M_WIDE) return le::invalid("le_moe_group: row tiles of %d or %d, got %d", TILE_M, TILE_M_WIDE, tile_m);
+  if (padded && slots_cap < max_tiles * tile_m) return le::invalid("le_moe_group: %d slots do not hold %d tiles of %d", slots_cap, max_tiles, tile_m);
   const size_t smem = sizeof(int32_t) * (3 * experts + 2);
   if (smem > 48 * 1024) return le::invalid("le_moe_group: too many experts (%d)", experts);
-  return le::launch_chained(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, pairs, experts, tile_m, slot_pair, tile_expert,
-                            tile_first, tile_rows, meta);
+  return le::launch_chained(moe_group_kernel, dim3(1), dim3(1024), smem, stream, ids, pairs, experts, tile_m, padded, max_tiles,
+                            slots_cap, slot_pair, pair_slot, tile_expert, tile_first, tile_rows, meta);
+}
+
+LE_API int le_moe_gather(void *out, const void *x, int64_t x_stride, int dtype, const int32_t *slot_pair, int src_div,
+                         int tile_m, const int32_t *meta, int slots_cap, int width, cudaStream_t stream) {
+  if (slots_cap <= 0) return 0;
+  const int piece = dtype == LE_BF16 ? 8 : 4;
+  if (width % piece || x_stride % piece || reinterpret_cast<uintptr_t>(out) % 16 || reinterpret_cast<uintptr_t>(x) % 16)
+    return le::invalid("le_moe_gather: rows in 16-byte pieces only");
+  if (dtype == LE_BF16)
+    return le::launch_chained(moe_gather_kernel<__nv_bfloat16>, dim3(slots_cap), dim3(128), 0, stream,
+                              static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(x), x_stride, slot_pair,
+                              src_div, tile_m, meta, width);
+  return le::launch_chained(moe_gather_kernel<float>, dim3(slots_cap), dim3(128), 0, stream, static_cast<float *>(out),
+                            static_cast<const float *>(x), x_stride, slot_pair, src_div, tile_m, meta, width);
+}
+
+LE_API int le_moe_combine_sorted(void *out, int dtype, const void *y, int y_dtype, const int32_t *pair_slot,
+                                 const float *share, const void *shared_out, const float *gate, int tokens, int width, int top,
+                                 cudaStream_t stream) {
+  const int64_t n = static_cast<int64_t>(tokens) * width;
+  if (n <= 0) return 0;
+  const dim3 grid(static_cast<unsigned>((n + 255) / 256)), block(256);
+  if (dtype == LE_BF16 && y_dtype == LE_F32)
+    return le::launch_chained(moe_combine_sorted_kernel<__nv_bfloat16, float>, grid, block, 0, stream,
+                              static_cast<__nv_bfloat16 *>(out), static_cast<const float *>(y), pair_slot, share,
+                              static_cast<const __nv_bfloat16 *>(shared_out), gate, n, width, top);
+  if (dtype == LE_BF16 && y_dtype == LE_BF16)
+    return le::launch_chained(moe_combine_sorted_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream,
+                              static_cast<__nv_bfloat16 *>(out), static_cast<const __nv_bfloat16 *>(y), pair_slot, share,
+                              static_cast<const __nv_bfloat16 *>(shared_out), gate, n, width, top);
+  if (dtype == LE_F32 && y_dtype == LE_F32)
+    return le::launch_chained(moe_combine_sorted_kernel<float, float>, grid, block, 0, stream, static_cast<float *>(out),
+                              static_cast<const float *>(y), pair_slot, share, static_cast<const float *>(shared_out), gate, n,
+                              width, top);
+  return le::invalid("le_moe_combine_sorted: no form for output type %d and rows of type %d", dtype, y_dtype);
 }
 
 // `max_tiles`: what the grid is sized for, pairs / tile_m + experts at most.  `tile_m`: the row tiles' size that

@@ -203,6 +203,23 @@ rope_pairs_store_vec_kernel(const T *__restrict__ src, int64_t src_stride, const
 // wide in `attn`, of which the first value_dim columns count), then, if
 // eps >= 0, o / sqrt(mean(o^2) + eps), then times `post`.  One warp per
 // (token, head).
+// VEC (1, 2, 4 or 8) consecutive elements as floats, in one access where VEC > 1.
+template <int VEC, typename T>
+__device__ __forceinline__ void loadv(const T *p, float (&v)[VEC]) {
+  struct __align__(sizeof(T) * VEC) Raw { T e[VEC]; };
+  const Raw raw = *reinterpret_cast<const Raw *>(p);
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) v[i] = le::to_f32(raw.e[i]);
+}
+template <int VEC, typename T>
+__device__ __forceinline__ void storev(T *p, const float (&v)[VEC]) {
+  struct __align__(sizeof(T) * VEC) Raw { T e[VEC]; };
+  Raw raw;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) raw.e[i] = le::from_f32<T>(v[i]);
+  *reinterpret_cast<Raw *>(p) = raw;
+}
+
 template <typename T, int VEC>
 __global__ void maps_combine_kernel(T *__restrict__ out, int64_t out_stride, const T *__restrict__ attn, int64_t attn_stride,
                                     const float *__restrict__ coef, int tokens, int heads, int segments, int head_dim,
@@ -219,14 +236,10 @@ __global__ void maps_combine_kernel(T *__restrict__ out, int64_t out_stride, con
     float v[VEC] = {};
     for (int m = 0; m < segments; ++m) {
       const float cm = coef[m];
-      if constexpr (VEC == 8) {
-        float x[8];
-        load8(a + m * head_dim + c, x);
+      float x[VEC];
+      loadv<VEC>(a + m * head_dim + c, x);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = fmaf(cm, x[i], v[i]);
-      } else {
-        v[0] = fmaf(cm, le::to_f32(a[m * head_dim + c]), v[0]);
-      }
+      for (int i = 0; i < VEC; ++i) v[i] = fmaf(cm, x[i], v[i]);
     }
 #pragma unroll
     for (int i = 0; i < VEC; ++i) sq += v[i] * v[i];
@@ -237,22 +250,14 @@ __global__ void maps_combine_kernel(T *__restrict__ out, int64_t out_stride, con
     float v[VEC] = {};
     for (int m = 0; m < segments; ++m) {
       const float cm = coef[m];
-      if constexpr (VEC == 8) {
-        float x[8];
-        load8(a + m * head_dim + c, x);
+      float x[VEC];
+      loadv<VEC>(a + m * head_dim + c, x);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = fmaf(cm, x[i], v[i]);
-      } else {
-        v[0] = fmaf(cm, le::to_f32(a[m * head_dim + c]), v[0]);
-      }
+      for (int i = 0; i < VEC; ++i) v[i] = fmaf(cm, x[i], v[i]);
     }
-    if constexpr (VEC == 8) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] *= factor;
-      store8(o + c, v);
-    } else {
-      o[c] = le::from_f32<T>(v[0] * factor);
-    }
+    for (int i = 0; i < VEC; ++i) v[i] *= factor;
+    storev<VEC>(o + c, v);
   }
 }
 
@@ -301,17 +306,28 @@ LE_API int le_maps_combine(void *out, int64_t out_stride, const void *attn, int6
   if (warps <= 0) return 0;
   const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
   const int elem = dtype == LE_BF16 ? 2 : 4;
-  const bool vec = value_dim % 8 == 0 && head_dim % 8 == 0 && out_stride % 8 == 0 && attn_stride % 8 == 0 &&
-                   reinterpret_cast<uintptr_t>(out) % (8 * elem) == 0 && reinterpret_cast<uintptr_t>(attn) % (8 * elem) == 0;
+  // the widest piece (8, 4 or 2 elements) that divides everything and still gives each of a warp's lanes one
+  int vec = 1;
+  for (int v = 8; v > 1; v >>= 1)
+    if (value_dim % v == 0 && head_dim % v == 0 && out_stride % v == 0 && attn_stride % v == 0 &&
+        reinterpret_cast<uintptr_t>(out) % (v * elem) == 0 && reinterpret_cast<uintptr_t>(attn) % (v * elem) == 0 &&
+        (value_dim / v >= 32 || v == 2)) {
+      vec = v;
+      break;
+    }
 #define LE_COMBINE(T, VEC)                                                                                                   \
   return le::launch_chained(maps_combine_kernel<T, VEC>, dim3(blocks), dim3(256), 0, stream, static_cast<T *>(out), out_stride, \
                             static_cast<const T *>(attn), attn_stride, coef, tokens, heads, segments, head_dim, value_dim, eps, \
                             post)
   if (dtype == LE_BF16) {
-    if (vec) LE_COMBINE(__nv_bfloat16, 8);
+    if (vec == 8) LE_COMBINE(__nv_bfloat16, 8);
+    if (vec == 4) LE_COMBINE(__nv_bfloat16, 4);
+    if (vec == 2) LE_COMBINE(__nv_bfloat16, 2);
     LE_COMBINE(__nv_bfloat16, 1);
   }
-  if (vec) LE_COMBINE(float, 8);
+  if (vec == 8) LE_COMBINE(float, 8);
+  if (vec == 4) LE_COMBINE(float, 4);
+  if (vec == 2) LE_COMBINE(float, 2);
   LE_COMBINE(float, 1);
 #undef LE_COMBINE
 }

@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int MAX_STREAMS = 8;
+constexpr int MOST_STREAMS = 8;
 
 template <typename T, int VEC> struct Pack;
 template <> struct Pack<float, 1> { float v; __device__ float get(int) const { return v; } __device__ void set(int, float x) { v = x; } };
@@ -37,7 +37,7 @@ template <> struct __align__(8) Pack<__nv_bfloat16, 4> {
 
 // VEC consecutive columns a thread and step (4: 16-byte accesses; the launcher sizes the block so that a row of up to
 // 2,048 columns is one step, every load of a thread in flight before its first store).
-template <typename TOut, typename TDelta, int VEC>
+template <typename TOut, typename TDelta, int VEC, int MAX_STREAMS>
 __global__ void __launch_bounds__(512)
 stream_norm_kernel(TOut *__restrict__ out, float *__restrict__ streams, const float *__restrict__ init,
                    const TDelta *__restrict__ delta, int parts, int64_t part_stride, const float *__restrict__ mix,
@@ -159,17 +159,24 @@ int launch_stream_norm(void *out, float *streams, const float *init, const void 
   auto aligned = [](const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
   const bool vec = W % 4 == 0 && aligned(out) && aligned(streams) && aligned(init) && aligned(delta) && aligned(weight) &&
                    aligned(bias) && part_stride % 4 == 0;
+  // few rows (a decode step): a thread per 16 bytes, so that a row is one round of loads; many rows: smaller blocks,
+  // several to a multiprocessor, which hide each other's rounds
+  int threads = vec ? (W / 4 + 31) / 32 * 32 : (W >= 1024 ? 256 : 128);
+  const int most = n <= 64 ? 512 : 256;
+  threads = threads > most ? most : threads;
+#define LE_STREAM_NORM(VEC, BOUND)                                                                                          \
+  return le::launch_chained(stream_norm_kernel<TOut, TDelta, VEC, BOUND>, dim3(n), dim3(threads), smem, stream,             \
+                            static_cast<TOut *>(out), streams, init, static_cast<const TDelta *>(delta), parts, part_stride, \
+                            mix, post, pre, weight, bias, rows, eps, W, S)
   if (vec) {
-    int threads = (W / 4 + 31) / 32 * 32;
-    threads = threads > 512 ? 512 : threads;
-    return le::launch_chained(stream_norm_kernel<TOut, TDelta, 4>, dim3(n), dim3(threads), smem, stream,
-                              static_cast<TOut *>(out), streams, init, static_cast<const TDelta *>(delta), parts, part_stride,
-                              mix, post, pre, weight, bias, rows, eps, W, S);
+    if (S == 1) LE_STREAM_NORM(4, 1);
+    if (S == 2) LE_STREAM_NORM(4, 2);
+    if (S <= 4) LE_STREAM_NORM(4, 4);
+    LE_STREAM_NORM(4, 8);
   }
-  const int threads = W >= 1024 ? 256 : 128;
-  return le::launch_chained(stream_norm_kernel<TOut, TDelta, 1>, dim3(n), dim3(threads), smem, stream, static_cast<TOut *>(out),
-                            streams, init, static_cast<const TDelta *>(delta), parts, part_stride, mix, post, pre, weight,
-                            bias, rows, eps, W, S);
+  if (S <= 4) LE_STREAM_NORM(1, 4);
+  LE_STREAM_NORM(1, 8);
+#undef LE_STREAM_NORM
 }
 
 }  // namespace
@@ -179,7 +186,7 @@ LE_API int le_stream_norm(void *out, int out_dtype, float *streams, const float 
                           const float *weight, const float *bias, const int32_t *rows, float eps, int n, int W, int S,
                           cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (S < 1 || S > MAX_STREAMS) return le::invalid("le_stream_norm: 1 to %d copies of the stream, got %d", MAX_STREAMS, S);
+  if (S < 1 || S > MOST_STREAMS) return le::invalid("le_stream_norm: 1 to %d copies of the stream, got %d", MOST_STREAMS, S);
   if (W < 1 || W > 11000) return le::invalid("le_stream_norm: rows of up to 11000 values, got %d", W);
   if (delta == nullptr) parts = 0;
   if (out_dtype == LE_BF16 && (delta == nullptr || delta_dtype == LE_BF16))

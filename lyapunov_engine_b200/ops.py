@@ -111,7 +111,13 @@ _CORE_SIGNATURES = {
     "le_moe_tile_rows": [c_int],
     "le_moe_route": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                      c_int, c_int, c_void_p],
-    "le_moe_group": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "le_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_void_p, c_void_p],
+    "le_moe_gather": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+    "le_moe_combine_sorted": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_void_p],
+    "le_gemm_tc_grouped_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int,
+                                c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p, c_void_p],
     "le_moe_grouped": [c_void_p, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_void_p, c_int,
                        c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                        c_float, c_float, c_void_p],
@@ -989,6 +995,8 @@ def softcap(logits, cap: float) -> None:
 # routed experts
 _moe_tile_rows: dict[bool, int] = {}
 MOE_WIDE_ROWS = 64      # rows an expert has on average from which the wide row tiles pay
+# 0: the experts' products of prompt portions stay on the mma.sync kernel (wide row tiles) instead of the tcgen05 one
+TC_EXPERTS = os.environ.get("LYAPUNOV_TC_EXPERTS", "1") not in ("0", "")
 
 
 def moe_tile_rows(wide: bool = False) -> int:
@@ -1027,16 +1035,66 @@ def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int) -> No
                                _ptr(ids), _ptr(weights), _ptr(gate), T, W, E, top, _stream()), "le_moe_route")
 
 
-def moe_group(ids, experts: int, slot_pair, tiles, meta, wide: bool = False) -> None:
+def moe_group(ids, experts: int, slot_pair, tiles, meta, wide: bool = False, padded: bool = False, pair_slot=None) -> None:
     """Sorts the pairs (entries of ``ids``) by expert: ``slot_pair`` int32
-    [pairs] lists the pairs expert by expert; ``tiles`` int32 [3, max tiles]
-    (expert, first slot, rows of each row tile); ``meta[0]`` the tile count."""
-    _need_cuda(ids, slot_pair, tiles, meta)
+    lists the pairs expert by expert; ``tiles`` int32 [3, max tiles] (expert,
+    first slot, rows of each row tile; unused entries zero); ``meta[0]`` the
+    tile count.  ``padded``: every expert's slots start at a multiple of the
+    tile's rows, slots that stand for no pair hold -1, and ``slot_pair`` has
+    room for max tiles * tile rows.  ``pair_slot`` (int32 [pairs]) receives
+    each pair's slot."""
+    _need_cuda(ids, slot_pair, tiles, meta, pair_slot)
     pairs = ids.numel()
     assert slot_pair.dtype == tiles.dtype == meta.dtype == torch.int32 and tiles.is_contiguous() and tiles.shape[0] == 3
-    assert slot_pair.numel() >= pairs and tiles.shape[1] >= moe_max_tiles(pairs, experts, wide)
-    _check(core().le_moe_group(_ptr(ids), pairs, experts, moe_tile_rows(wide), _ptr(slot_pair), _ptr(tiles[0]), _ptr(tiles[1]),
+    max_tiles = tiles.shape[1]
+    assert max_tiles >= moe_max_tiles(pairs, experts, wide)
+    assert slot_pair.numel() >= (max_tiles * moe_tile_rows(wide) if padded else pairs)
+    assert pair_slot is None or (pair_slot.dtype == torch.int32 and pair_slot.numel() >= pairs)
+    _check(core().le_moe_group(_ptr(ids), pairs, experts, moe_tile_rows(wide), 1 if padded else 0, max_tiles,
+                               slot_pair.numel(), _ptr(slot_pair), _ptr(pair_slot), _ptr(tiles[0]), _ptr(tiles[1]),
                                _ptr(tiles[2]), _ptr(meta), _stream()), "le_moe_group")
+
+
+def moe_gather(out, x, slot_pair, meta, src_div: int, wide: bool = True) -> None:
+    """out[slot] = x[slot_pair[slot] // src_div] for the slots of the first
+    meta[0] row tiles (zeros where a slot stands for no pair)."""
+    _need_cuda(out, x, slot_pair, meta)
+    assert out.dtype == x.dtype and out.is_contiguous() and x.stride(1) == 1 and out.shape[1] == x.shape[1]
+    assert slot_pair.numel() >= out.shape[0]
+    _check(core().le_moe_gather(_ptr(out), _ptr(x), x.stride(0), dtype_code(x.dtype), _ptr(slot_pair), int(src_div),
+                                moe_tile_rows(wide), _ptr(meta), out.shape[0], x.shape[1], _stream()), "le_moe_gather")
+
+
+def moe_combine_sorted(out, y, pair_slot, share, top: int, shared_out=None, gate=None) -> None:
+    """out[t] = sum_j share[t, j] * y[pair_slot[t * top + j]] (+ gate[t] * shared_out[t])."""
+    _need_cuda(out, y, pair_slot, share, shared_out, gate)
+    T, W = out.shape
+    assert y.is_contiguous() and y.shape[1] == W and out.is_contiguous() and share.dtype == torch.float32
+    assert share.is_contiguous() and share.numel() == T * top and pair_slot.dtype == torch.int32 and pair_slot.numel() >= T * top
+    assert shared_out is None or (shared_out.dtype == out.dtype and shared_out.is_contiguous() and shared_out.shape == out.shape)
+    _check(core().le_moe_combine_sorted(_ptr(out), dtype_code(out.dtype), _ptr(y), dtype_code(y.dtype), _ptr(pair_slot),
+                                        _ptr(share), _ptr(shared_out), _ptr(gate), T, W, top, _stream()),
+           "le_moe_combine_sorted")
+
+
+def gemm_tc_grouped(out, a, w, tile_expert, tile_count, gated: bool = False, status=None, activation=(0, 1.0, 0.0)) -> None:
+    """The tcgen05 / TMA product in its grouped form: ``a`` [M, K] holds row
+    tiles of 128 rows, tile m is multiplied with matrix ``tile_expert[m]`` of
+    ``w`` [experts, N, K] (gated: N = 2 F, gate rows then up rows, out =
+    act(gate, up)), and only the first ``tile_count[0]`` tiles are computed;
+    both lists are int32 on the device."""
+    _need_cuda(out, a, w, tile_expert, tile_count)
+    E, N, K = w.shape
+    M = a.shape[0]
+    assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.is_contiguous() and a.shape[1] == K and M % 128 == 0
+    assert out.shape == (M, N // 2 if gated else N) and out.stride(1) == 1 and a.stride(1) == 1
+    assert tile_expert.dtype == torch.int32 and tile_expert.numel() >= M // 128 and tile_count.dtype == torch.int32
+    if status is None:
+        status = tc_status(a.device)
+    _check(core().le_gemm_tc_grouped_bf16(_ptr(out), dtype_code(out.dtype), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(1),
+                                          out.stride(0), E, _ptr(tile_expert), _ptr(tile_count), 1 if gated else 0,
+                                          int(activation[0]), float(activation[1]), float(activation[2]), _ptr(status),
+                                          _stream()), "le_gemm_tc_grouped_bf16")
 
 
 def moe_grouped(out, a, w, slot_pair, tiles, meta, max_tiles: int, src_div: int, scatter: bool, pair_weight=None,

@@ -83,9 +83,26 @@ class RoutedExperts(FeedForward):
         ops.moe_route(ids, share, gate, x, self.w_router, self.b_router, self.w_shared_gate, top)
         wide = ops.moe_wide_tiles(pairs, E, rt.dtype, W, F)
         max_tiles = ops.moe_max_tiles(pairs, E, wide)
-        slot_pair = ws.get("moe_slots", (pairs,), torch.int32)
         tiles = ws.get("moe_tiles", (3, max_tiles), torch.int32)
         meta = ws.get("moe_meta", (4,), torch.int32)
+        shared_out = self.shared.forward_plain(x, ctx) if self.shared is not None else None
+        out = ws.get("ffn_out", (T, W), rt.dtype)
+        if wide and ops.TC_EXPERTS and ops.tc_applies(x, self.w_gate_up[0]):
+            # many rows per expert: whole tiles of 128 sorted rows through the tcgen05 product
+            rows = max_tiles * ops.moe_tile_rows(True)
+            slot_pair = ws.get("moe_slots", (rows,), torch.int32)
+            pair_slot = ws.get("moe_pair_slots", (pairs,), torch.int32)
+            ops.moe_group(ids, E, slot_pair, tiles, meta, True, padded=True, pair_slot=pair_slot)
+            x_sorted = ws.get("moe_x_sorted", (rows, W), rt.dtype)
+            ops.moe_gather(x_sorted, x, slot_pair, meta, top)
+            act = ws.get("moe_act", (rows, F), rt.dtype)
+            ops.gemm_tc_grouped(act, x_sorted, self.w_gate_up, tiles[0], meta, gated=True, status=ctx.status,
+                                activation=self.activation)
+            y = ws.get("moe_y", (rows, W), torch.float32)
+            ops.gemm_tc_grouped(y, act, self.w_down, tiles[0], meta, status=ctx.status)
+            ops.moe_combine_sorted(out, y, pair_slot, share, top, shared_out, gate)
+            return out
+        slot_pair = ws.get("moe_slots", (pairs,), torch.int32)
         ops.moe_group(ids, E, slot_pair, tiles, meta, wide)
         act = ws.get("moe_act", (pairs, F), rt.dtype)
         ops.moe_grouped(act, x, self.w_gate_up, slot_pair, tiles, meta, max_tiles, src_div=top, scatter=False, gated=True,
@@ -93,7 +110,5 @@ class RoutedExperts(FeedForward):
         y = ws.get("moe_y", (pairs, W), torch.float32)
         ops.moe_grouped(y, act, self.w_down, slot_pair, tiles, meta, max_tiles, src_div=0, scatter=True,
                         pair_weight=share.view(-1), wide=wide)
-        shared_out = self.shared.forward_plain(x, ctx) if self.shared is not None else None
-        out = ws.get("ffn_out", (T, W), rt.dtype)
         ops.moe_combine(out, y, top, shared_out, gate)
         return out

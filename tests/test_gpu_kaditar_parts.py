@@ -286,6 +286,35 @@ def test_routed_experts_step_by_step(T, W, E, top, F, shared, dtype):
         want = want + torch.sigmoid(h.double() @ sg.double())[:, None] * shared_out.double()
     tol = dict(atol=1e-4, rtol=1e-4) if dtype == torch.float32 else dict(atol=4e-2, rtol=4e-2)
     torch.testing.assert_close(out.float().cpu(), want.float(), **tol)
+    if dtype == torch.bfloat16 and W % 8 == 0 and F % 8 == 0:
+        # the form for many rows per expert: slots padded to whole tiles of 128, rows gathered, the tcgen05 product
+        # in its grouped form twice, the weighted sum through each pair's slot
+        max_tiles = ops.moe_max_tiles(pairs, E, True)
+        rows = max_tiles * ops.moe_tile_rows(True)
+        slots = torch.full((rows,), 12345, dtype=torch.int32, device=DEV)
+        pair_slot = torch.full((pairs,), -7, dtype=torch.int32, device=DEV)
+        tiles = torch.full((3, max_tiles), 99, dtype=torch.int32, device=DEV)
+        ops.moe_group(ids, E, slots, tiles, meta, True, padded=True, pair_slot=pair_slot)
+        n_tiles = int(meta[0])
+        sl, ps = slots.cpu(), pair_slot.cpu()
+        assert sorted(ps.tolist()) == sorted(i for i in range(n_tiles * 128) if sl[i] >= 0) and len(set(ps.tolist())) == pairs
+        for pair in range(pairs):
+            slot = int(ps[pair])
+            assert int(sl[slot]) == pair and int(tiles[0, slot // 128]) == int(flat[pair])
+        assert all(int(v) in (-1,) or 0 <= int(v) < pairs for v in sl[:n_tiles * 128])
+        status = ops.new_status(DEV)
+        x_sorted = torch.full((rows, W), 3.0, dtype=dtype, device=DEV)
+        ops.moe_gather(x_sorted, h.to(DEV), slots, meta, top)
+        for pair in (0, pairs // 2, pairs - 1):
+            assert torch.equal(x_sorted[int(ps[pair])].cpu(), h[pair // top])
+        act2 = torch.zeros(rows, F, dtype=dtype, device=DEV)
+        ops.gemm_tc_grouped(act2, x_sorted, wgu, tiles[0], meta, gated=True, status=status, activation=(ops.GLU_SILU, 1.0, 0.0))
+        y2 = torch.zeros(rows, W, device=DEV)
+        ops.gemm_tc_grouped(y2, act2, wd, tiles[0], meta, status=status)
+        ops.check_status(status)
+        out2 = torch.zeros(T, W, dtype=dtype, device=DEV)
+        ops.moe_combine_sorted(out2, y2, pair_slot, share, top, shared_out.to(DEV) if shared else None, gate if shared else None)
+        torch.testing.assert_close(out2.float().cpu(), want.float(), **tol)
 
 
 def test_router_prefers_the_lower_index_on_a_tie_and_ignores_the_rest():
