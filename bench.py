@@ -1129,7 +1129,7 @@ def kaditar_kernel_rows(pk, llama):
 
     status = ops.new_status(dev)
     ws = Workspace(dev)
-    for T in (8, 2048):
+    for T in (1, 8, 2048):
         S = cfg["streams"]
         nbytes = T * W * (8 * S + 2 + 2) + 8 * W
         n = sets_for(nbytes)
@@ -1184,25 +1184,44 @@ def kaditar_kernel_rows(pk, llama):
         pairs = T * top
         wide = ops.moe_wide_tiles(pairs, E, bf, W, F)
         max_tiles = ops.moe_max_tiles(pairs, E, wide)
-        slots = torch.zeros(pairs, dtype=torch.int32, device=dev)
         tiles = torch.zeros(3, max_tiles, dtype=torch.int32, device=dev)
         meta = torch.zeros(4, dtype=torch.int32, device=dev)
-        row("pairs grouped by expert", "", T, pairs * 8, lambda i: ops.moe_group(ids, E, slots, tiles, meta, wide), 2)
         wgu = torch.randn(E, 2 * F, W, device=dev).to(bf) * 0.02
         wd = torch.randn(E, W, F, device=dev).to(bf) * 0.02
-        act = torch.empty(pairs, F, device=dev, dtype=bf)
-        y = torch.empty(pairs, W, device=dev)
         used = min(E, pairs)
-        row("experts' gate/up product, silu", "gate/up product, silu", T, 2 * (used * 2 * F * W + T * W + pairs * F),
-            lambda i: ops.moe_grouped(act, x[i % 4], wgu, slots, tiles, meta, max_tiles, src_div=top, scatter=False, gated=True, wide=wide), 4,
-            flops=2 * pairs * 2 * F * W)
-        row("experts' down product, weighted", "down product", T, 2 * (used * F * W + pairs * F) + 4 * pairs * W,
-            lambda i: ops.moe_grouped(y, act, wd, slots, tiles, meta, max_tiles, src_div=0, scatter=True, pair_weight=share.view(-1), wide=wide), 2,
-            flops=2 * pairs * F * W)
         shared_out = torch.randn(T, W, device=dev).to(bf)
         o2 = torch.empty(T, W, device=dev, dtype=bf)
-        row("experts' outputs summed + gated shared expert", "", T, pairs * W * 4 + T * W * 4,
-            lambda i: ops.moe_combine(o2, y, top, shared_out, gate), 2)
+        if wide:
+            # many rows per expert: slots padded to whole tiles, rows gathered, the tcgen05 product in its grouped form
+            cap = max_tiles * ops.moe_tile_rows(True)
+            slots = torch.zeros(cap, dtype=torch.int32, device=dev)
+            pair_slot = torch.zeros(pairs, dtype=torch.int32, device=dev)
+            row("pairs grouped by expert, slots padded to tiles", "", T, pairs * 12,
+                lambda i: ops.moe_group(ids, E, slots, tiles, meta, True, padded=True, pair_slot=pair_slot), 2)
+            xs = torch.zeros(cap, W, device=dev, dtype=bf)
+            row("rows gathered into slot order", "", T, 2 * 2 * pairs * W, lambda i: ops.moe_gather(xs, x[i % 4], slots, meta, top), 4)
+            act = torch.empty(cap, F, device=dev, dtype=bf)
+            y = torch.empty(cap, W, device=dev, dtype=bf)
+            row("experts' gate/up product, silu (tcgen05, grouped)", "gate/up product, silu", T,
+                2 * (used * 2 * F * W + pairs * W + pairs * F),
+                lambda i: ops.gemm_tc_grouped(act, xs, wgu, tiles[0], meta, gated=True, status=status), 2, flops=2 * pairs * 2 * F * W)
+            row("experts' down product (tcgen05, grouped)", "down product", T, 2 * (used * F * W + pairs * F + pairs * W),
+                lambda i: ops.gemm_tc_grouped(y, act, wd, tiles[0], meta, status=status), 2, flops=2 * pairs * F * W)
+            row("experts' outputs weighted and summed + gated shared expert", "", T, pairs * W * 2 + T * W * 4,
+                lambda i: ops.moe_combine_sorted(o2, y, pair_slot, share, top, shared_out, gate), 2)
+        else:
+            slots = torch.zeros(pairs, dtype=torch.int32, device=dev)
+            row("pairs grouped by expert", "", T, pairs * 8, lambda i: ops.moe_group(ids, E, slots, tiles, meta, wide), 2)
+            act = torch.empty(pairs, F, device=dev, dtype=bf)
+            y = torch.empty(pairs, W, device=dev)
+            row("experts' gate/up product, silu (mma.sync)", "gate/up product, silu", T, 2 * (used * 2 * F * W + T * W + pairs * F),
+                lambda i: ops.moe_grouped(act, x[i % 4], wgu, slots, tiles, meta, max_tiles, src_div=top, scatter=False, gated=True, wide=wide), 4,
+                flops=2 * pairs * 2 * F * W)
+            row("experts' down product, weighted (mma.sync)", "down product", T, 2 * (used * F * W + pairs * F) + 4 * pairs * W,
+                lambda i: ops.moe_grouped(y, act, wd, slots, tiles, meta, max_tiles, src_div=0, scatter=True, pair_weight=share.view(-1), wide=wide), 2,
+                flops=2 * pairs * F * W)
+            row("experts' outputs summed + gated shared expert", "", T, pairs * W * 4 + T * W * 4,
+                lambda i: ops.moe_combine(o2, y, top, shared_out, gate), 2)
         # the like products of the dense path, with the rows and sizes the chosen experts have together
         wl = torch.randn(2 * top * F, W, device=dev).to(bf) * 0.02
         al = torch.empty(T, top * F, device=dev, dtype=bf)

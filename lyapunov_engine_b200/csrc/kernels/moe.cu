@@ -4,8 +4,8 @@
 // route:   z = Wr h + b in 32 bits (Wr, b float32; h in the activations'
 //          type), the `top` largest z (ties: the lower index), their weights
 //          softmax over the chosen z only; and, where given, one more number
-//          per token, sigmoid(sg . h), for a shared expert.  A block takes
-//          eight tokens; each of its warps a row of the router for all of them.
+//          per token, sigmoid(sg . h), for a shared expert.  A block takes up
+//          to eight tokens; each of its warps a row of the router for all.
 // group:   pair p = t * top + j goes to expert id[p].  Counting sort in one
 //          block: offsets per expert, the pairs in expert order, and a list of
 //          row tiles (expert, first sorted slot, rows), each tile within one
@@ -32,97 +32,103 @@ constexpr int TILE_M_WIDE = 128;  // of the tensor-core kernel where experts hav
 constexpr int TILE_N = 64;   // output columns per block
 constexpr int TILE_K = 32;
 
-constexpr int ROUTE_TOKENS = 8;   // tokens a block routes: a warp takes a row of the router for all of them
 constexpr int ROUTE_WARPS = 16;
+constexpr int ROUTE_SMEM_FLOATS = 16 * 1024;   // of the tokens' rows a block holds as float32
 
-__device__ __forceinline__ void load4(const float *p, float (&v)[4]) {
-  const float4 a = *reinterpret_cast<const float4 *>(p);
-  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-}
-__device__ __forceinline__ void load4(const __nv_bfloat16 *p, float (&v)[4]) {
-  const uint2 raw = *reinterpret_cast<const uint2 *>(p);
-  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
-  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-}
-
-template <typename T>
+// A block routes NT tokens: their rows are turned into float32 in shared memory once; then a warp takes a row of the
+// router (or the shared gate's row) for all NT tokens, 16 bytes of it a lane and step; then a warp per token picks.
+template <typename T, int NT>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restrict__ w_router,
                  const float *__restrict__ b_router, const float *__restrict__ w_gate, int32_t *__restrict__ ids,
                  float *__restrict__ weights, float *__restrict__ gate, int tokens, int width, int experts, int top) {
-  extern __shared__ float smem[];       // z [ROUTE_TOKENS][experts + 1]
+  extern __shared__ __align__(16) float smem[];       // x [NT][width], z [NT][experts + 1]
+  float *xs = smem;
+  float *zs = smem + NT * width;
   le::let_successor_start();
   le::wait_for_predecessor();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * ROUTE_TOKENS;
-  const int nt = tokens - t0 < ROUTE_TOKENS ? tokens - t0 : ROUTE_TOKENS;
+  const int t0 = blockIdx.x * NT;
+  const int nt = tokens - t0 < NT ? tokens - t0 : NT;
   const int ld = experts + 1;
   const int rows = experts + (w_gate != nullptr ? 1 : 0);
-  const T *x = h + static_cast<int64_t>(t0) * h_stride;
-  const bool pieces = width % 4 == 0 && h_stride % 4 == 0 && reinterpret_cast<uintptr_t>(h) % 16 == 0 &&
-                      reinterpret_cast<uintptr_t>(w_router) % 16 == 0 && reinterpret_cast<uintptr_t>(w_gate) % 16 == 0;
+  for (int i = threadIdx.x; i < NT * width; i += blockDim.x) {
+    const int j = i / width, c = i - j * width;
+    xs[i] = j < nt ? le::to_f32(h[static_cast<int64_t>(t0 + j) * h_stride + c]) : 0.0f;
+  }
+  __syncthreads();
+  const bool pieces = width % 4 == 0 && reinterpret_cast<uintptr_t>(w_router) % 16 == 0 && reinterpret_cast<uintptr_t>(w_gate) % 16 == 0;
   for (int r = warp; r < rows; r += ROUTE_WARPS) {
     const float *w = r < experts ? w_router + static_cast<int64_t>(r) * width : w_gate;
-    float acc[ROUTE_TOKENS] = {};
+    float acc[NT] = {};
     if (pieces) {
 #pragma unroll 4
       for (int c = lane * 4; c < width; c += 128) {
         const float4 wv = *reinterpret_cast<const float4 *>(w + c);
 #pragma unroll
-        for (int j = 0; j < ROUTE_TOKENS; ++j)
-          if (j < nt) {
-            float xv[4];
-            load4(x + j * h_stride + c, xv);
-            acc[j] = fmaf(xv[0], wv.x, fmaf(xv[1], wv.y, fmaf(xv[2], wv.z, fmaf(xv[3], wv.w, acc[j]))));
-          }
+        for (int j = 0; j < NT; ++j) {
+          const float4 xv = *reinterpret_cast<const float4 *>(xs + j * width + c);
+          acc[j] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc[j]))));
+        }
       }
     } else {
-#pragma unroll 2
       for (int c = lane; c < width; c += 32) {
         const float wv = w[c];
 #pragma unroll
-        for (int j = 0; j < ROUTE_TOKENS; ++j)
-          if (j < nt) acc[j] = fmaf(le::to_f32(x[j * h_stride + c]), wv, acc[j]);
+        for (int j = 0; j < NT; ++j) acc[j] = fmaf(xs[j * width + c], wv, acc[j]);
       }
     }
 #pragma unroll
-    for (int j = 0; j < ROUTE_TOKENS; ++j) {
+    for (int j = 0; j < NT; ++j) {
       const float v = le::warp_sum(acc[j]);
-      if (lane == 0) smem[j * ld + r] = v + (r < experts && b_router != nullptr ? b_router[r] : 0.0f);
+      if (lane == 0) zs[j * ld + r] = v + (r < experts && b_router != nullptr ? b_router[r] : 0.0f);
     }
   }
   __syncthreads();
-  if (warp >= nt) return;
-  const int t = t0 + warp;
-  float *z = smem + warp * ld;
-  if (w_gate != nullptr && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[experts]));
-  float first = 0.0f, total = 0.0f;
-  for (int j = 0; j < top; ++j) {
-    float best = -INFINITY;
-    int at = 0x7fffffff;
-    for (int e = lane; e < experts; e += 32) {
-      const float v = z[e];
-      if (v > best || (v == best && e < at)) { best = v; at = e; }
-    }
+  for (int jt = warp; jt < nt; jt += ROUTE_WARPS) {
+    const int t = t0 + jt;
+    float *z = zs + jt * ld;
+    if (w_gate != nullptr && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[experts]));
+    float first = 0.0f, total = 0.0f;
+    for (int j = 0; j < top; ++j) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int e = lane; e < experts; e += 32) {
+        const float v = z[e];
+        if (v > best || (v == best && e < at)) { best = v; at = e; }
+      }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-      if (ov > best || (ov == best && oa < at)) { best = ov; at = oa; }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (ov > best || (ov == best && oa < at)) { best = ov; at = oa; }
+      }
+      if (at == 0x7fffffff) at = 0;   // (no finite logit left: cannot happen with top <= experts)
+      if (j == 0) first = best;
+      const float p = expf(best - first);
+      total += p;
+      if (lane == 0) {
+        ids[static_cast<int64_t>(t) * top + j] = at;
+        weights[static_cast<int64_t>(t) * top + j] = p;
+        z[at] = -INFINITY;
+      }
+      __syncwarp();
     }
-    if (at == 0x7fffffff) at = 0;   // (no finite logit left: cannot happen with top <= experts)
-    if (j == 0) first = best;
-    const float p = expf(best - first);
-    total += p;
-    if (lane == 0) {
-      ids[static_cast<int64_t>(t) * top + j] = at;
-      weights[static_cast<int64_t>(t) * top + j] = p;
-      z[at] = -INFINITY;
-    }
-    __syncwarp();
+    for (int j = lane; j < top; j += 32) weights[static_cast<int64_t>(t) * top + j] /= total;
   }
-  for (int j = lane; j < top; j += 32) weights[static_cast<int64_t>(t) * top + j] /= total;
+}
+
+template <typename T, int NT>
+int launch_route(const void *h, int64_t h_stride, const float *w_router, const float *b_router, const float *w_gate,
+                 int32_t *ids, float *weights, float *gate, int tokens, int width, int experts, int top, cudaStream_t stream) {
+  auto kernel = moe_route_kernel<T, NT>;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(NT) * width + NT * (experts + 1));
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return le::invalid("le_moe_route: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  }
+  return le::launch_chained(kernel, dim3((tokens + NT - 1) / NT), dim3(ROUTE_WARPS * 32), smem, stream, static_cast<const T *>(h),
+                            h_stride, w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top);
 }
 
 // One block.  meta[0] = number of tiles.  `padded`: every expert's slots start at a multiple of tile_m (slots that
@@ -302,15 +308,11 @@ __global__ void moe_grouped_kernel(TOut *__restrict__ out, int64_t out_stride, c
 
 
 // ---- the same products on the tensor cores (bfloat16 inputs, mma.sync m16n8k16, float32 sums) ----
-// A block takes one row tile (TM sorted slots of one expert) and 64 output columns (gated: the 64 gate rows and the
-// 64 up rows of W that make them).  Slots are the 16-row operand, W's rows the 8-column one; a warp owns 32 slots x
-// WN columns.  K runs in steps of 32 through two cp.async stages; rows of A are gathered through the slot list, rows
+// A block takes one row tile (TM sorted slots of one expert) and TN output columns (gated: the TN gate rows and the
+// TN up rows of W that make them).  Slots are the 16-row operand, W's rows the 8-column one; a warp owns 32 slots x
+// WN columns.  K runs in steps through a ring of cp.async stages; rows of A are gathered through the slot list, rows
 // beyond the tile and columns beyond K are filled with zeros by the copy itself.  K must be a multiple of 8 and all
 // rows 16-byte aligned.
-constexpr int MMA_TN = 64;
-constexpr int MMA_TK = 32;
-constexpr int MMA_LD = MMA_TK + 8;   // bf16 elements per shared-memory row: 80 bytes, fragment loads free of bank conflicts
-
 __device__ __forceinline__ void cp_async_16(void *smem, const void *gmem, int src_bytes) {
   const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(src_bytes) : "memory");
@@ -325,21 +327,42 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <int TM, typename TOut, bool GATED>
-__global__ void __launch_bounds__(TM == 32 ? 128 : 256)
+// Two shapes.  Narrow (TM = 32 slots x 32 columns, K in steps of 64, four stages): few rows per expert, the product
+// is bound by streaming W, so blocks are many and each keeps three stages of W in flight.  Wide (128 x 64, steps of
+// 32, two stages): many rows per expert, where the tcgen05 product is not taken.
+// Few (shape 16: the same 32 slots, named by its columns): a handful of row tiles in all (one or two decoded tokens),
+// where only many small blocks with long steps of K keep the memory system busy.
+template <int TM> struct MmaShape;
+template <> struct MmaShape<32> { static constexpr int ROWS = 32, TN = 32, TK = 64, STAGES = 4, THREADS = 128, WARPS_M = 1; };
+template <> struct MmaShape<128> { static constexpr int ROWS = 128, TN = 64, TK = 32, STAGES = 2, THREADS = 256, WARPS_M = 4; };
+template <> struct MmaShape<16> { static constexpr int ROWS = 32, TN = 16, TK = 128, STAGES = 4, THREADS = 64, WARPS_M = 1; };
+
+template <int SHAPE, bool GATED>
+constexpr size_t mma_smem_bytes() {
+  using S = MmaShape<SHAPE>;
+  return static_cast<size_t>(S::STAGES) * (S::ROWS + (GATED ? 2 : 1) * S::TN) * (S::TK + 8) * sizeof(__nv_bfloat16);
+}
+
+template <int SHAPE, typename TOut, bool GATED>
+__global__ void __launch_bounds__(MmaShape<SHAPE>::THREADS)
 moe_grouped_mma_kernel(TOut *__restrict__ out, int64_t out_stride, const __nv_bfloat16 *__restrict__ a, int64_t a_stride,
                        const __nv_bfloat16 *__restrict__ w, int64_t expert_stride, int64_t w_stride,
                        const int32_t *__restrict__ slot_pair, int src_div, int scatter, const float *__restrict__ pair_weight,
                        const int32_t *__restrict__ tile_expert, const int32_t *__restrict__ tile_first,
                        const int32_t *__restrict__ tile_rows, const int32_t *__restrict__ meta, int N, int K,
                        le::GatedActivation act) {
-  constexpr int THREADS = TM == 32 ? 128 : 256;
-  constexpr int WARPS_M = TM / 32;                 // 1 or 4
-  constexpr int WN = TM == 32 ? 16 : 32;           // columns a warp owns
-  constexpr int NT = WN / 8;                       // its 8-column tiles
+  using S = MmaShape<SHAPE>;
+  constexpr int TM = S::ROWS, TN = S::TN, TK = S::TK, STAGES = S::STAGES, THREADS = S::THREADS, WARPS_M = S::WARPS_M;
+  constexpr int LD = TK + 8;                        // bf16 elements per shared-memory row: fragment loads free of bank conflicts
+  constexpr int PIECES = TK / 8;                    // 16-byte pieces of a row of a stage
+  constexpr int WARPS_N = THREADS / 32 / WARPS_M;
+  constexpr int WN = TN / WARPS_N;                  // columns a warp owns
+  constexpr int NT = WN / 8;                        // its 8-column tiles
   constexpr int WPARTS = GATED ? 2 : 1;
-  __shared__ __align__(16) __nv_bfloat16 a_s[2][TM][MMA_LD];
-  __shared__ __align__(16) __nv_bfloat16 w_s[2][WPARTS][MMA_TN][MMA_LD];
+  constexpr int W_ROWS = WPARTS * TN;
+  extern __shared__ __align__(16) unsigned char mma_smem[];
+  __nv_bfloat16 *a_s = reinterpret_cast<__nv_bfloat16 *>(mma_smem);            // [STAGES][TM][LD]
+  __nv_bfloat16 *w_s = a_s + STAGES * TM * LD;                                 // [STAGES][W_ROWS][LD]
   __shared__ int32_t src_row[TM], dst_row[TM];
   __shared__ float row_factor[TM];
   le::let_successor_start();
@@ -347,7 +370,7 @@ moe_grouped_mma_kernel(TOut *__restrict__ out, int64_t out_stride, const __nv_bf
   const int tile = blockIdx.y;
   if (tile >= meta[0]) return;
   const int expert = tile_expert[tile], first = tile_first[tile], rows = tile_rows[tile];
-  const int n0 = blockIdx.x * MMA_TN;
+  const int n0 = blockIdx.x * TN;
   for (int i = threadIdx.x; i < TM; i += THREADS) {
     int src = 0, dst = 0;
     float f = 1.0f;
@@ -365,52 +388,54 @@ moe_grouped_mma_kernel(TOut *__restrict__ out, int64_t out_stride, const __nv_bf
   const __nv_bfloat16 *w_e = w + static_cast<int64_t>(expert) * expert_stride;
 
   auto load_stage = [&](int stage, int k0) {
-    // 16-byte pieces: a row of a stage holds 4 of them
-    for (int i = threadIdx.x; i < TM * 4; i += THREADS) {
-      const int m = i >> 2, piece = i & 3, k = k0 + piece * 8;
-      const bool in = m < rows && k < K;
-      cp_async_16(&a_s[stage][m][piece * 8], in ? a + static_cast<int64_t>(src_row[m]) * a_stride + k : a, in ? 16 : 0);
+    // rows of x: only those the tile has (the others' shared memory is never read into a stored result)
+    for (int i = threadIdx.x; i < TM * PIECES; i += THREADS) {
+      const int m = i / PIECES, piece = i - m * PIECES, k = k0 + piece * 8;
+      if (m >= rows) continue;
+      const bool in = k < K;
+      cp_async_16(a_s + (stage * TM + m) * LD + piece * 8, in ? a + static_cast<int64_t>(src_row[m]) * a_stride + k : a, in ? 16 : 0);
     }
-    for (int i = threadIdx.x; i < WPARTS * MMA_TN * 4; i += THREADS) {
-      const int part = i / (MMA_TN * 4), r = (i >> 2) % MMA_TN, piece = i & 3, k = k0 + piece * 8;
-      const bool in = n0 + r < N && k < K;
-      cp_async_16(&w_s[stage][part][r][piece * 8],
-                  in ? w_e + static_cast<int64_t>(part * N + n0 + r) * w_stride + k : w_e, in ? 16 : 0);
+    for (int i = threadIdx.x; i < W_ROWS * PIECES; i += THREADS) {
+      const int r = i / PIECES, piece = i - r * PIECES, k = k0 + piece * 8;
+      const int part = r / TN, n = n0 + r - part * TN;
+      const bool in = n < N && k < K;
+      cp_async_16(w_s + (stage * W_ROWS + r) * LD + piece * 8,
+                  in ? w_e + static_cast<int64_t>(part * N + n) * w_stride + k : w_e, in ? 16 : 0);
     }
-    cp_async_commit();
   };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t4 = lane & 3;
   const int wm = (warp % WARPS_M) * 32, wn = (warp / WARPS_M) * WN;
   float acc[WPARTS][2][NT][4] = {};
-  const int steps = (K + MMA_TK - 1) / MMA_TK;
-  load_stage(0, 0);
-  for (int s = 0; s < steps; ++s) {
-    if (s + 1 < steps) {
-      load_stage((s + 1) & 1, (s + 1) * MMA_TK);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
-    const int st = s & 1;
+  const int steps = (K + TK - 1) / TK;
 #pragma unroll
-    for (int kk = 0; kk < MMA_TK; kk += 16) {
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < steps) load_stage(s, s * TK);
+    cp_async_commit();
+  }
+  for (int s = 0; s < steps; ++s) {
+    cp_async_wait<STAGES - 2>();           // step s has landed
+    __syncthreads();                       // ... for everyone, and everyone is done with step s - 1
+    if (s + STAGES - 1 < steps) load_stage((s + STAGES - 1) % STAGES, (s + STAGES - 1) * TK);
+    cp_async_commit();
+    const int st = s % STAGES;
+#pragma unroll
+    for (int kk = 0; kk < TK; kk += 16) {
       uint32_t af[2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
-        const __nv_bfloat16 *base = &a_s[st][wm + mt * 16][kk];
-        af[mt][0] = *reinterpret_cast<const uint32_t *>(base + (g)*MMA_LD + 2 * t4);
-        af[mt][1] = *reinterpret_cast<const uint32_t *>(base + (g + 8) * MMA_LD + 2 * t4);
-        af[mt][2] = *reinterpret_cast<const uint32_t *>(base + (g)*MMA_LD + 2 * t4 + 8);
-        af[mt][3] = *reinterpret_cast<const uint32_t *>(base + (g + 8) * MMA_LD + 2 * t4 + 8);
+        const __nv_bfloat16 *base = a_s + (st * TM + wm + mt * 16) * LD + kk;
+        af[mt][0] = *reinterpret_cast<const uint32_t *>(base + (g)*LD + 2 * t4);
+        af[mt][1] = *reinterpret_cast<const uint32_t *>(base + (g + 8) * LD + 2 * t4);
+        af[mt][2] = *reinterpret_cast<const uint32_t *>(base + (g)*LD + 2 * t4 + 8);
+        af[mt][3] = *reinterpret_cast<const uint32_t *>(base + (g + 8) * LD + 2 * t4 + 8);
       }
 #pragma unroll
       for (int part = 0; part < WPARTS; ++part)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          const __nv_bfloat16 *base = &w_s[st][part][wn + nt * 8 + g][kk];
+          const __nv_bfloat16 *base = w_s + (st * W_ROWS + part * TN + wn + nt * 8 + g) * LD + kk;
           uint32_t bf[2];
           bf[0] = *reinterpret_cast<const uint32_t *>(base + 2 * t4);
           bf[1] = *reinterpret_cast<const uint32_t *>(base + 2 * t4 + 8);
@@ -418,8 +443,8 @@ moe_grouped_mma_kernel(TOut *__restrict__ out, int64_t out_stride, const __nv_bf
           mma_bf16_16816(acc[part][1][nt], af[1], bf);
         }
     }
-    __syncthreads();
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -439,6 +464,22 @@ moe_grouped_mma_kernel(TOut *__restrict__ out, int64_t out_stride, const __nv_bf
           o[n] = le::from_f32<TOut>(v * f);
         }
     }
+}
+
+template <int TM, typename TOut, bool GATED, typename... Args>
+int launch_grouped_mma(int N, int max_tiles, cudaStream_t stream, Args... args) {
+  auto kernel = moe_grouped_mma_kernel<TM, TOut, GATED>;
+  constexpr size_t smem = mma_smem_bytes<TM, GATED>();
+  if (smem > 48 * 1024) {
+    static bool raised = false;          // once per form and process
+    if (!raised) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return le::invalid("le_moe_grouped: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      raised = true;
+    }
+  }
+  const dim3 grid((N + MmaShape<TM>::TN - 1) / MmaShape<TM>::TN, max_tiles);
+  return le::launch_chained(kernel, grid, dim3(MmaShape<TM>::THREADS), smem, stream, args...);
 }
 
 template <typename T>
@@ -464,15 +505,22 @@ LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float 
                         int top, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (top < 1 || top > experts) return le::invalid("le_moe_route: %d of %d experts", top, experts);
-  const size_t smem = sizeof(float) * ROUTE_TOKENS * (experts + 1);
-  if (smem > 48 * 1024) return le::invalid("le_moe_route: up to %d experts, got %d", 48 * 1024 / (4 * ROUTE_TOKENS) - 1, experts);
-  const dim3 grid((tokens + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(ROUTE_WARPS * 32);
-  if (dtype == LE_BF16)
-    return le::launch_chained(moe_route_kernel<__nv_bfloat16>, grid, block, smem, stream,
-                              static_cast<const __nv_bfloat16 *>(h), h_stride, w_router, b_router, w_gate, ids, weights, gate,
-                              tokens, width, experts, top);
-  return le::launch_chained(moe_route_kernel<float>, grid, block, smem, stream, static_cast<const float *>(h), h_stride,
-                            w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top);
+  // tokens a block takes: up to 8, fewer where the step has fewer or a row is wide
+  int nt = 8;
+  while (nt > 1 && (nt / 2 >= tokens || nt * width > ROUTE_SMEM_FLOATS)) nt >>= 1;
+  if (static_cast<size_t>(width + experts + 1) * 4 > 200 * 1024) return le::invalid("le_moe_route: rows of %d values and %d experts do not fit", width, experts);
+#define LE_ROUTE(T, NT) return launch_route<T, NT>(h, h_stride, w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top, stream)
+  if (dtype == LE_BF16) {
+    if (nt == 8) LE_ROUTE(__nv_bfloat16, 8);
+    if (nt == 4) LE_ROUTE(__nv_bfloat16, 4);
+    if (nt == 2) LE_ROUTE(__nv_bfloat16, 2);
+    LE_ROUTE(__nv_bfloat16, 1);
+  }
+  if (nt == 8) LE_ROUTE(float, 8);
+  if (nt == 4) LE_ROUTE(float, 4);
+  if (nt == 2) LE_ROUTE(float, 2);
+  LE_ROUTE(float, 1);
+#undef LE_ROUTE
 }
 
 LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int tile_m, int padded, int max_tiles, int slots_cap,
@@ -538,13 +586,17 @@ LE_API int le_moe_grouped(void *out, int out_dtype, int64_t out_stride, const vo
   const bool aligned = K % 8 == 0 && a_stride % 8 == 0 && w_stride % 8 == 0 && expert_stride % 8 == 0 &&
                        reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
   if (dtype == LE_BF16 && aligned && (tile_m == TILE_M || tile_m == TILE_M_WIDE)) {
-    const dim3 mgrid((N + MMA_TN - 1) / MMA_TN, max_tiles);
-#define LE_MOE_MMA(TM, TOut, GATED)                                                                                           \
-  return le::launch_chained(moe_grouped_mma_kernel<TM, TOut, GATED>, mgrid, dim3(TM == 32 ? 128 : 256), 0, stream,            \
-                            static_cast<TOut *>(out), out_stride, static_cast<const __nv_bfloat16 *>(a), a_stride,            \
-                            static_cast<const __nv_bfloat16 *>(w), expert_stride, w_stride, slot_pair, src_div, scatter,      \
-                            pair_weight, tile_expert, tile_first, tile_rows, meta, N, K, act)
-    if (tile_m == TILE_M) {
+#define LE_MOE_MMA(TM, TOut, GATED)                                                                                        \
+  return launch_grouped_mma<TM, TOut, GATED>(N, max_tiles, stream, static_cast<TOut *>(out), out_stride,                   \
+                                             static_cast<const __nv_bfloat16 *>(a), a_stride,                              \
+                                             static_cast<const __nv_bfloat16 *>(w), expert_stride, w_stride, slot_pair,    \
+                                             src_div, scatter, pair_weight, tile_expert, tile_first, tile_rows, meta, N, K, \
+                                             act)
+    if (tile_m == TILE_M && max_tiles <= 4) {
+      if (gated && out_dtype == LE_BF16) LE_MOE_MMA(16, __nv_bfloat16, true);
+      if (!gated && out_dtype == LE_F32) LE_MOE_MMA(16, float, false);
+      if (!gated && out_dtype == LE_BF16) LE_MOE_MMA(16, __nv_bfloat16, false);
+    } else if (tile_m == TILE_M) {
       if (gated && out_dtype == LE_BF16) LE_MOE_MMA(32, __nv_bfloat16, true);
       if (!gated && out_dtype == LE_F32) LE_MOE_MMA(32, float, false);
       if (!gated && out_dtype == LE_BF16) LE_MOE_MMA(32, __nv_bfloat16, false);

@@ -98,7 +98,7 @@ class RoutedExperts(FeedForward):
             act = ws.get("moe_act", (rows, F), rt.dtype)
             ops.gemm_tc_grouped(act, x_sorted, self.w_gate_up, tiles[0], meta, gated=True, status=ctx.status,
                                 activation=self.activation)
-            y = ws.get("moe_y", (rows, W), torch.float32)
+            y = ws.get("moe_y_sorted", (rows, W), rt.dtype)
             ops.gemm_tc_grouped(y, act, self.w_down, tiles[0], meta, status=ctx.status)
             ops.moe_combine_sorted(out, y, pair_slot, share, top, shared_out, gate)
             return out
