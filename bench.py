@@ -1179,8 +1179,9 @@ def kaditar_kernel_rows(pk, llama):
         ids = torch.zeros(T, top, dtype=torch.int32, device=dev)
         share = torch.zeros(T, top, device=dev)
         gate = torch.zeros(T, device=dev)
+        zbuf = torch.zeros(T * (E + 1), device=dev)
         row("router: logits, top, softmax, shared gate", "", T, T * W * 2 + 4 * (E + 1) * W,
-            lambda i: ops.moe_route(ids, share, gate, x[i % 4], wr, br, sg, top), 4)
+            lambda i: ops.moe_route(ids, share, gate, x[i % 4], wr, br, sg, top, scratch=zbuf), 4)
         pairs = T * top
         wide = ops.moe_wide_tiles(pairs, E, bf, W, F)
         max_tiles = ops.moe_max_tiles(pairs, E, wide)

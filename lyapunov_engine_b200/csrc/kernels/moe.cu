@@ -4,8 +4,8 @@
 // route:   z = Wr h + b in 32 bits (Wr, b float32; h in the activations'
 //          type), the `top` largest z (ties: the lower index), their weights
 //          softmax over the chosen z only; and, where given, one more number
-//          per token, sigmoid(sg . h), for a shared expert.  A block takes up
-//          to eight tokens; each of its warps a row of the router for all.
+//          per token, sigmoid(sg . h), for a shared expert.  Two kernels: the
+//          logits (blocks over tokens and over rows of the router), the choice.
 // group:   pair p = t * top + j goes to expert id[p].  Counting sort in one
 //          block: offsets per expert, the pairs in expert order, and a list of
 //          row tiles (expert, first sorted slot, rows), each tile within one
@@ -35,16 +35,29 @@ constexpr int TILE_K = 32;
 constexpr int ROUTE_WARPS = 16;
 constexpr int ROUTE_SMEM_FLOATS = 16 * 1024;   // of the tokens' rows a block holds as float32
 
-// A block routes NT tokens: their rows are turned into float32 in shared memory once; then a warp takes a row of the
-// router (or the shared gate's row) for all NT tokens, 16 bytes of it a lane and step; then a warp per token picks.
-template <typename T, int NT>
+// Four consecutive activations in one access, as floats.
+template <typename T> struct RoutePiece;
+template <> struct RoutePiece<float> { using type = float4; };
+template <> struct RoutePiece<__nv_bfloat16> { using type = uint2; };
+__device__ __forceinline__ void unpack4(const float4 &a, float (&v)[4]) { v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; }
+__device__ __forceinline__ void unpack4(const uint2 &raw, float (&v)[4]) {
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+  const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+// Router logits.  A block takes NT tokens and RB rows of the router (the shared gate's row counts as one more): the
+// tokens' rows are turned into float32 in shared memory once; warp w takes row w % RB and every (16 / RB)-th piece of
+// 128 columns, 16 bytes a lane, for all NT tokens; the slices' sums are added in a fixed order.  z is [tokens, experts + 1].
+template <typename T, int NT, int RB>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
-moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restrict__ w_router,
-                 const float *__restrict__ b_router, const float *__restrict__ w_gate, int32_t *__restrict__ ids,
-                 float *__restrict__ weights, float *__restrict__ gate, int tokens, int width, int experts, int top) {
-  extern __shared__ __align__(16) float smem[];       // x [NT][width], z [NT][experts + 1]
+moe_logits_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restrict__ w_router,
+                  const float *__restrict__ b_router, const float *__restrict__ w_gate, float *__restrict__ z, int tokens,
+                  int width, int experts) {
+  constexpr int KS = ROUTE_WARPS / RB;
+  extern __shared__ __align__(16) float smem[];       // x [NT][width], partial sums [NT][RB][KS]
   float *xs = smem;
-  float *zs = smem + NT * width;
+  float *part = smem + NT * width;
   le::let_successor_start();
   le::wait_for_predecessor();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -52,18 +65,30 @@ moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restr
   const int nt = tokens - t0 < NT ? tokens - t0 : NT;
   const int ld = experts + 1;
   const int rows = experts + (w_gate != nullptr ? 1 : 0);
-  for (int i = threadIdx.x; i < NT * width; i += blockDim.x) {
-    const int j = i / width, c = i - j * width;
-    xs[i] = j < nt ? le::to_f32(h[static_cast<int64_t>(t0 + j) * h_stride + c]) : 0.0f;
+  if (width % 4 == 0 && h_stride % 4 == 0 && reinterpret_cast<uintptr_t>(h) % 16 == 0) {
+    const int quads = width >> 2;
+    for (int i = threadIdx.x; i < NT * quads; i += blockDim.x) {
+      const int j = i / quads, c = (i - j * quads) << 2;
+      float v[4] = {};
+      if (j < nt) unpack4(*reinterpret_cast<const typename RoutePiece<T>::type *>(h + static_cast<int64_t>(t0 + j) * h_stride + c), v);
+      *reinterpret_cast<float4 *>(xs + j * width + c) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < NT * width; i += blockDim.x) {
+      const int j = i / width, c = i - j * width;
+      xs[i] = j < nt ? le::to_f32(h[static_cast<int64_t>(t0 + j) * h_stride + c]) : 0.0f;
+    }
   }
   __syncthreads();
-  const bool pieces = width % 4 == 0 && reinterpret_cast<uintptr_t>(w_router) % 16 == 0 && reinterpret_cast<uintptr_t>(w_gate) % 16 == 0;
-  for (int r = warp; r < rows; r += ROUTE_WARPS) {
+  const int rb = warp % RB, slice = warp / RB;
+  const int r = blockIdx.y * RB + rb;
+  float acc[NT] = {};
+  if (r < rows) {
     const float *w = r < experts ? w_router + static_cast<int64_t>(r) * width : w_gate;
-    float acc[NT] = {};
+    const bool pieces = width % 4 == 0 && reinterpret_cast<uintptr_t>(w) % 16 == 0;
     if (pieces) {
 #pragma unroll 4
-      for (int c = lane * 4; c < width; c += 128) {
+      for (int c = (slice * 32 + lane) * 4; c < width; c += KS * 128) {
         const float4 wv = *reinterpret_cast<const float4 *>(w + c);
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
@@ -72,63 +97,83 @@ moe_route_kernel(const T *__restrict__ h, int64_t h_stride, const float *__restr
         }
       }
     } else {
-      for (int c = lane; c < width; c += 32) {
+      for (int c = slice * 32 + lane; c < width; c += KS * 32) {
         const float wv = w[c];
 #pragma unroll
         for (int j = 0; j < NT; ++j) acc[j] = fmaf(xs[j * width + c], wv, acc[j]);
       }
     }
+  }
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      const float v = le::warp_sum(acc[j]);
-      if (lane == 0) zs[j * ld + r] = v + (r < experts && b_router != nullptr ? b_router[r] : 0.0f);
-    }
+  for (int j = 0; j < NT; ++j) {
+    const float v = le::warp_sum(acc[j]);
+    if (lane == 0) part[(j * RB + rb) * KS + slice] = v;
   }
   __syncthreads();
-  for (int jt = warp; jt < nt; jt += ROUTE_WARPS) {
-    const int t = t0 + jt;
-    float *z = zs + jt * ld;
-    if (w_gate != nullptr && lane == 0) gate[t] = 1.0f / (1.0f + expf(-z[experts]));
-    float first = 0.0f, total = 0.0f;
-    for (int j = 0; j < top; ++j) {
-      float best = -INFINITY;
-      int at = 0x7fffffff;
-      for (int e = lane; e < experts; e += 32) {
-        const float v = z[e];
-        if (v > best || (v == best && e < at)) { best = v; at = e; }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-        if (ov > best || (ov == best && oa < at)) { best = ov; at = oa; }
-      }
-      if (at == 0x7fffffff) at = 0;   // (no finite logit left: cannot happen with top <= experts)
-      if (j == 0) first = best;
-      const float p = expf(best - first);
-      total += p;
-      if (lane == 0) {
-        ids[static_cast<int64_t>(t) * top + j] = at;
-        weights[static_cast<int64_t>(t) * top + j] = p;
-        z[at] = -INFINITY;
-      }
-      __syncwarp();
-    }
-    for (int j = lane; j < top; j += 32) weights[static_cast<int64_t>(t) * top + j] /= total;
+  for (int i = threadIdx.x; i < NT * RB; i += blockDim.x) {
+    const int j = i / RB, b = i - j * RB, row = blockIdx.y * RB + b;
+    if (j >= nt || row >= rows) continue;
+    float v = 0.0f;
+    for (int k = 0; k < KS; ++k) v += part[(j * RB + b) * KS + k];
+    if (row < experts && b_router != nullptr) v += b_router[row];
+    z[static_cast<int64_t>(t0 + j) * ld + row] = v;
   }
 }
 
-template <typename T, int NT>
-int launch_route(const void *h, int64_t h_stride, const float *w_router, const float *b_router, const float *w_gate,
-                 int32_t *ids, float *weights, float *gate, int tokens, int width, int experts, int top, cudaStream_t stream) {
-  auto kernel = moe_route_kernel<T, NT>;
-  const size_t smem = sizeof(float) * (static_cast<size_t>(NT) * width + NT * (experts + 1));
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (e != cudaSuccess) return le::invalid("le_moe_route: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+// The choice: a warp per token picks the `top` largest of its logits (ties: the lower index), writes their ids and
+// the softmax over them, and the shared gate's sigmoid.  It marks what it has picked in z.
+__global__ void moe_pick_kernel(float *__restrict__ z, int32_t *__restrict__ ids, float *__restrict__ weights,
+                                float *__restrict__ gate, int tokens, int experts, int top, int with_gate) {
+  le::let_successor_start();
+  le::wait_for_predecessor();
+  const int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (t >= tokens) return;
+  float *zt = z + static_cast<int64_t>(t) * (experts + 1);
+  if (with_gate && lane == 0) gate[t] = 1.0f / (1.0f + expf(-zt[experts]));
+  float first = 0.0f, total = 0.0f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = zt[e];
+      if (v > best || (v == best && e < at)) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ov > best || (ov == best && oa < at)) { best = ov; at = oa; }
+    }
+    if (at == 0x7fffffff) at = 0;   // (no finite logit left: cannot happen with top <= experts)
+    if (j == 0) first = best;
+    const float p = expf(best - first);
+    total += p;
+    if (lane == 0) {
+      ids[static_cast<int64_t>(t) * top + j] = at;
+      weights[static_cast<int64_t>(t) * top + j] = p;
+      zt[at] = -INFINITY;
+    }
+    __syncwarp();
   }
-  return le::launch_chained(kernel, dim3((tokens + NT - 1) / NT), dim3(ROUTE_WARPS * 32), smem, stream, static_cast<const T *>(h),
-                            h_stride, w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top);
+  for (int j = lane; j < top; j += 32) weights[static_cast<int64_t>(t) * top + j] /= total;
+}
+
+template <typename T, int NT, int RB>
+int launch_logits(const void *h, int64_t h_stride, const float *w_router, const float *b_router, const float *w_gate, float *z,
+                  int tokens, int width, int experts, cudaStream_t stream) {
+  auto kernel = moe_logits_kernel<T, NT, RB>;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(NT) * width + NT * ROUTE_WARPS);
+  if (smem > 48 * 1024) {
+    static size_t raised = 0;            // per form and process: the most asked for so far
+    if (smem > raised) {
+      cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (e != cudaSuccess) return le::invalid("le_moe_route: cannot get %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      raised = smem;
+    }
+  }
+  const int rows = experts + (w_gate != nullptr ? 1 : 0);
+  return le::launch_chained(kernel, dim3((tokens + NT - 1) / NT, (rows + RB - 1) / RB), dim3(ROUTE_WARPS * 32), smem, stream,
+                            static_cast<const T *>(h), h_stride, w_router, b_router, w_gate, z, tokens, width, experts);
 }
 
 // One block.  meta[0] = number of tiles.  `padded`: every expert's slots start at a multiple of tile_m (slots that
@@ -500,27 +545,38 @@ __global__ void moe_combine_kernel(T *__restrict__ out, const float *__restrict_
 
 LE_API int le_moe_tile_rows(int wide) { return wide ? TILE_M_WIDE : TILE_M; }
 
+// `z`: float32 scratch [tokens, experts + 1] (the logits; the picked ones are overwritten).
 LE_API int le_moe_route(const void *h, int64_t h_stride, int dtype, const float *w_router, const float *b_router,
-                        const float *w_gate, int32_t *ids, float *weights, float *gate, int tokens, int width, int experts,
-                        int top, cudaStream_t stream) {
+                        const float *w_gate, float *z, int32_t *ids, float *weights, float *gate, int tokens, int width,
+                        int experts, int top, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (top < 1 || top > experts) return le::invalid("le_moe_route: %d of %d experts", top, experts);
   // tokens a block takes: up to 8, fewer where the step has fewer or a row is wide
   int nt = 8;
   while (nt > 1 && (nt / 2 >= tokens || nt * width > ROUTE_SMEM_FLOATS)) nt >>= 1;
-  if (static_cast<size_t>(width + experts + 1) * 4 > 200 * 1024) return le::invalid("le_moe_route: rows of %d values and %d experts do not fit", width, experts);
-#define LE_ROUTE(T, NT) return launch_route<T, NT>(h, h_stride, w_router, b_router, w_gate, ids, weights, gate, tokens, width, experts, top, stream)
+  if (static_cast<size_t>(width) * 4 > 200 * 1024) return le::invalid("le_moe_route: rows of %d values do not fit", width);
+  // rows of the router a block takes: all 16 of a round where the tokens alone make enough blocks, else one row a
+  // block with its warps sharing out the columns
+  const bool many = (tokens + nt - 1) / nt >= 32;
+  int rc;
+#define LE_LOGITS(T, NT)                                                                                                  \
+  rc = many ? launch_logits<T, NT, 16>(h, h_stride, w_router, b_router, w_gate, z, tokens, width, experts, stream)        \
+            : launch_logits<T, NT, 1>(h, h_stride, w_router, b_router, w_gate, z, tokens, width, experts, stream)
   if (dtype == LE_BF16) {
-    if (nt == 8) LE_ROUTE(__nv_bfloat16, 8);
-    if (nt == 4) LE_ROUTE(__nv_bfloat16, 4);
-    if (nt == 2) LE_ROUTE(__nv_bfloat16, 2);
-    LE_ROUTE(__nv_bfloat16, 1);
+    if (nt == 8) { LE_LOGITS(__nv_bfloat16, 8); }
+    else if (nt == 4) { LE_LOGITS(__nv_bfloat16, 4); }
+    else if (nt == 2) { LE_LOGITS(__nv_bfloat16, 2); }
+    else { LE_LOGITS(__nv_bfloat16, 1); }
+  } else {
+    if (nt == 8) { LE_LOGITS(float, 8); }
+    else if (nt == 4) { LE_LOGITS(float, 4); }
+    else if (nt == 2) { LE_LOGITS(float, 2); }
+    else { LE_LOGITS(float, 1); }
   }
-  if (nt == 8) LE_ROUTE(float, 8);
-  if (nt == 4) LE_ROUTE(float, 4);
-  if (nt == 2) LE_ROUTE(float, 2);
-  LE_ROUTE(float, 1);
-#undef LE_ROUTE
+#undef LE_LOGITS
+  if (rc != 0) return rc;
+  return le::launch_chained(moe_pick_kernel, dim3((tokens + 7) / 8), dim3(256), 0, stream, z, ids, weights, gate, tokens, experts,
+                            top, w_gate != nullptr ? 1 : 0);
 }
 
 LE_API int le_moe_group(const int32_t *ids, int pairs, int experts, int tile_m, int padded, int max_tiles, int slots_cap,

@@ -109,8 +109,8 @@ _CORE_SIGNATURES = {
                         c_float, c_void_p],
     "le_softcap": [c_void_p, c_int64, c_float, c_void_p],
     "le_moe_tile_rows": [c_int],
-    "le_moe_route": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                     c_int, c_int, c_void_p],
+    "le_moe_route": [c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                     c_int, c_int, c_int, c_void_p],
     "le_moe_group": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p],
     "le_moe_gather": [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
@@ -1017,12 +1017,14 @@ def moe_max_tiles(pairs: int, experts: int, wide: bool = False) -> int:
     return pairs // moe_tile_rows(wide) + min(experts, pairs)
 
 
-def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int) -> None:
+def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int, scratch=None) -> None:
     """Per row of ``h``: router logits W h + b in 32 bits, the ``top`` largest
     (``ids`` int32 [T, top], best first), softmax over the chosen logits
     (``weights`` float32 [T, top]); with ``w_gate`` (float32 [W]) also
-    ``gate`` [T] = sigmoid(w_gate . h)."""
-    _need_cuda(ids, weights, gate, h, w_router, b_router, w_gate)
+    ``gate`` [T] = sigmoid(w_gate . h).  ``scratch``: float32, T * (experts +
+    1) elements, for the logits (made here when not given: a caller whose
+    steps are captured passes its own)."""
+    _need_cuda(ids, weights, gate, h, w_router, b_router, w_gate, scratch)
     T, W = h.shape
     E = w_router.shape[0]
     assert w_router.dtype == torch.float32 and w_router.is_contiguous() and w_router.shape[1] == W and h.stride(1) == 1
@@ -1031,8 +1033,12 @@ def moe_route(ids, weights, gate, h, w_router, b_router, w_gate, top: int) -> No
     assert weights.dtype == torch.float32 and weights.is_contiguous() and tuple(weights.shape) == (T, top)
     if w_gate is not None:
         assert w_gate.dtype == torch.float32 and w_gate.numel() == W and gate.dtype == torch.float32 and gate.numel() >= T
+    if scratch is None:
+        scratch = torch.empty(T * (E + 1), dtype=torch.float32, device=h.device)
+    assert scratch.dtype == torch.float32 and scratch.is_contiguous() and scratch.numel() >= T * (E + 1)
     _check(core().le_moe_route(_ptr(h), h.stride(0), dtype_code(h.dtype), _ptr(w_router), _ptr(b_router), _ptr(w_gate),
-                               _ptr(ids), _ptr(weights), _ptr(gate), T, W, E, top, _stream()), "le_moe_route")
+                               _ptr(scratch), _ptr(ids), _ptr(weights), _ptr(gate), T, W, E, top, _stream()), "le_moe_route",
+           launches=2)
 
 
 def moe_group(ids, experts: int, slot_pair, tiles, meta, wide: bool = False, padded: bool = False, pair_slot=None) -> None:

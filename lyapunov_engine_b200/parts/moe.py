@@ -80,7 +80,8 @@ class RoutedExperts(FeedForward):
         ids = ws.get("moe_ids", (T, top), torch.int32)
         share = ws.get("moe_share", (T, top), torch.float32)
         gate = ws.get("moe_shared_gate", (T,), torch.float32) if self.w_shared_gate is not None else None
-        ops.moe_route(ids, share, gate, x, self.w_router, self.b_router, self.w_shared_gate, top)
+        logits = ws.get("moe_logits", (T * (E + 1),), torch.float32)
+        ops.moe_route(ids, share, gate, x, self.w_router, self.b_router, self.w_shared_gate, top, scratch=logits)
         wide = ops.moe_wide_tiles(pairs, E, rt.dtype, W, F)
         max_tiles = ops.moe_max_tiles(pairs, E, wide)
         tiles = ws.get("moe_tiles", (3, max_tiles), torch.int32)
