@@ -1030,7 +1030,7 @@ def kaditar_config(llama: dict, window: int = 2048) -> dict:
     chosen experts and shared expert together have the dense layer's size."""
     nh, nkv, hd, I = llama["num_attention_heads"], llama["num_key_value_heads"], llama["head_dim"], llama["intermediate_size"]
     mixer = {"heads": nh, "kv_heads": nkv, "dim": hd // 2, "vdim": hd, "scale": (hd // 2) ** -0.5, "diff": 0.3,
-             "rot": {"dims": hd // 4, "base": 500000.0}, "mask": {"size": window}}
+             "rot": {"dims": hd // 4, "base": float(llama["rope_theta"])}, "mask": {"size": window}}
     dense = {"kind": "dense", "ff": I}
     routed = {"kind": "moe", "expert": {"ff": I // 4}, "router": {"experts": 16, "top": 2}, "shared": {"ff": I // 2}}
     return {"architecture": "Kaditar", "vocab": llama["vocab_size"], "width": llama["hidden_size"], "norm": {"eps": 1e-5},

@@ -14,7 +14,7 @@ DEV = "cuda:0"
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("W,S,parts", [(96, 3, 0), (192, 4, 2), (100, 1, 1), (2048, 2, 0), (66, 8, 3), (4096, 4, 1)])
+@pytest.mark.parametrize("W,S,parts", [(96, 3, 0), (208, 4, 2), (100, 1, 1), (2048, 2, 0), (66, 8, 3), (4096, 4, 1)])
 def test_stream_copies_update_read_and_layer_norm(W, S, parts, dtype):
     from lyapunov_engine_b200 import ops
     g = torch.Generator().manual_seed(W + S)
@@ -59,7 +59,7 @@ def test_stream_copies_update_read_and_layer_norm(W, S, parts, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,segs,d,e,rot,base", [(4, 2, 2, 48, 96, 24, 5e5), (2, 1, 2, 20, 12, 10, 1e4), (3, 3, 1, 16, 16, 16, 1e4),
+@pytest.mark.parametrize("H,G,segs,d,e,rot,base", [(4, 2, 2, 40, 80, 16, 1e6), (2, 1, 2, 20, 12, 10, 1e4), (3, 3, 1, 16, 16, 16, 1e4),
                                                    (2, 2, 2, 8, 40, 0, 1.0), (1, 1, 3, 10, 7, 6, 50.0)])
 def test_rotary_pairs_bias_spread_queries_and_cache_write(H, G, segs, d, e, rot, base, dtype):
     from lyapunov_engine_b200 import ops
@@ -120,7 +120,7 @@ def test_rotary_pairs_bias_spread_queries_and_cache_write(H, G, segs, d, e, rot,
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,segs,hd,e", [(4, 2, 96, 96), (3, 2, 48, 12), (1, 2, 16, 7), (2, 3, 64, 40)])
+@pytest.mark.parametrize("H,segs,hd,e", [(4, 2, 80, 80), (3, 2, 48, 12), (1, 2, 16, 7), (2, 3, 64, 40)])
 def test_maps_of_a_head_combined(H, segs, hd, e, dtype):
     from lyapunov_engine_b200 import ops
     g = torch.Generator().manual_seed(hd + e)
@@ -224,7 +224,7 @@ def test_relu_gate_in_every_gated_kernel(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("T,W,E,top,F,shared", [(5, 64, 6, 2, 24, 40), (70, 192, 16, 2, 64, 128), (9, 100, 3, 3, 20, 0),
+@pytest.mark.parametrize("T,W,E,top,F,shared", [(5, 64, 6, 2, 24, 40), (70, 176, 12, 2, 56, 120), (9, 100, 3, 3, 20, 0),
                                                 (33, 72, 1, 1, 16, 0), (300, 128, 40, 4, 36, 0), (700, 64, 4, 2, 200, 0)])
 def test_routed_experts_step_by_step(T, W, E, top, F, shared, dtype):
     """Router, grouping, both products and the weighted sum, each against plain
